@@ -47,6 +47,8 @@ class LineView:
     state: Optional[torch.Tensor]   # [slots, *shape] or None
     writes: bool = True
     has_values: bool = True         # False: ``v`` is ``k`` (a line that keeps one row per position)
+    index: int = -1                 # which cache line this is (a key for what layers hand each other within a step)
+    has_readers: bool = False       # another scheduled layer reads this line after its writer (set by the model)
 
 
 class CacheGroup:
@@ -230,10 +232,10 @@ class KVCache:
         if line not in self._line_group:
             if st is None:
                 return None
-            return LineView(None, None, None, 0, PAGE, self.lengths_dev, st, writes)
+            return LineView(None, None, None, 0, PAGE, self.lengths_dev, st, writes, index=line)
         gi, li = self._line_group[line]
         g = self.groups[gi]
-        return LineView(g.k[li], g.v[li], g.table_dev, g.ring, PAGE, self.lengths_dev, st, writes, g.need.values)
+        return LineView(g.k[li], g.v[li], g.table_dev, g.ring, PAGE, self.lengths_dev, st, writes, g.need.values, index=line)
 
     def bytes(self) -> int:
         return sum(g.bytes() for g in self.groups) + sum(t.numel() * t.element_size() for t in self.state.values())

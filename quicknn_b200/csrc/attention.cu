@@ -87,7 +87,7 @@ attn_decode_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict
                    const int* __restrict__ page_table, int max_pages, int page_size, int ring,
                    const int* __restrict__ slots, const int* __restrict__ slot_len, int nq, int nkv, int hd, int LPT,
                    float scale, float cap, int window, float* __restrict__ part_o, float* __restrict__ part_ml,
-                   int n_splits) {
+                   int n_splits, const float* __restrict__ slopes) {
     pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     extern __shared__ float smem[];  // [DEC_WARPS][GT][hd + 2]
@@ -117,10 +117,11 @@ attn_decode_kernel(const T* __restrict__ q, size_t q_stride, const T* __restrict
         const int begin = kbeg + split * per;
         const int end = min(begin + per, n);
         if (begin < end) {
-            float qr[GT][CPL][VEC];
+            float qr[GT][CPL][VEC], sl[GT];
             load_query<T, CPL, GT>(q + (size_t)b * q_stride + (size_t)kh * G * hd, hd, G, gt0, LPT, chunks, scale, qr);
+            load_slopes<GT>(slopes, kh * G, G, gt0, sl);
             PagedKV<T> kv{k_pool, v_pool, page_table + (size_t)slot * max_pages, page_size, nkv, hd, ring, kh};
-            attend_range<T, CPL, GT>(qr, kv, begin, end, warp * TPW, DEC_WARPS * TPW, LPT, chunks, cap, m, l, o);
+            attend_range<T, CPL, GT>(qr, kv, begin, end, warp * TPW, DEC_WARPS * TPW, LPT, chunks, cap, sl, n - 1, m, l, o);
         }
     }
     merge_groups<CPL, GT, VEC>(LPT, m, l, o);
@@ -155,7 +156,8 @@ attn_decode_tiled_kernel(const T* __restrict__ q, size_t q_stride, const T* __re
                          const T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
                          int page_size, int ring, const int* __restrict__ slots, const int* __restrict__ slot_len,
                          int nq, int nkv, int hd, int LPT, float scale, float cap, int window,
-                         float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
+                         float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits,
+                         const float* __restrict__ slopes) {
     pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     constexpr int NV = GT * TT;
@@ -213,6 +215,7 @@ attn_decode_tiled_kernel(const T* __restrict__ q, size_t q_stride, const T* __re
             __syncthreads();
             const int first = begin + warp * tile, stride = DEC_WARPS * tile;
             const int my_tiles = first < end ? (end - first + stride - 1) / stride : 0;
+            const float my_slope = (slopes != nullptr && gt0 + my_g < G) ? slopes[kh * G + gt0 + my_g] : 0.f;
 
             // fetch tile `it` of this warp into stage it % DEC_STAGES
             auto fetch = [&](int it) {
@@ -285,8 +288,10 @@ attn_decode_tiled_kernel(const T* __restrict__ q, size_t q_stride, const T* __re
                 float sc = s[0];
                 for (; d >= 1; d >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, d);
                 // this lane now owns the score of (head my_g, key my_tt of the tile)
-                const bool mine = (base + my_tt * TPW + grp) < end;
-                sc = mine ? softcap_t<T>(sc, cap) : -CUDART_INF_F;
+                const int my_key = base + my_tt * TPW + grp;
+                const bool mine = my_key < end;
+                // the bias of the distance to the newest position, by this lane's head's slope (0: none)
+                sc = mine ? softcap_t<T>(sc, cap) - my_slope * (float)(n - 1 - my_key) : -CUDART_INF_F;
                 float tmax = sc;
                 for (int off = R; off < R * TT; off <<= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, off));
                 float m_old = m[0];
@@ -442,7 +447,7 @@ extern "C" int qnn_attn_decode_mma_split(const void* q, long long q_stride, cons
                                          const int* slots, const int* slot_len, int B, int nq, int nkv, int hd,
                                          float scale, float cap, int window, float* part_o, float* part_ml,
                                          int n_splits, void* out, long long out_stride, int* combined,
-                                         cudaStream_t st);
+                                         const float* slopes, cudaStream_t st);
 
 // threads of the combine kernel's block: a group of hd/4 threads for every key range, up to 1024; and the
 // groups that such a block has (see attn_combine_kernel)
@@ -465,7 +470,7 @@ static int decode_launch(const void* q, long long q_stride, const void* k_pool, 
                          const int* page_table, int max_pages, int page_size, int ring, const int* slots,
                          const int* slot_len, int B, int nq, int nkv, int hd, float scale, float cap, int window,
                          float* part_o, float* part_ml, int n_splits, void* out, long long out_stride,
-                         cudaStream_t st) {
+                         const float* slopes, cudaStream_t st) {
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
     const Geometry geo = geometry<T>(hd, nq / nkv);
     if (!geo.ok) return QNN_ERR_UNSUPPORTED;
@@ -476,7 +481,7 @@ static int decode_launch(const void* q, long long q_stride, const void* k_pool, 
     if (smem > 48 * 1024) return QNN_ERR_UNSUPPORTED;
 #define QNN_DEC_ARGS                                                                                              \
     (const T*)q, (size_t)q_stride, (const T*)k_pool, (const T*)v_pool, page_table, max_pages, page_size, ring, slots, \
-        slot_len, nq, nkv, hd, geo.lpt, scale, cap, window, part_o, part_ml, n_splits
+        slot_len, nq, nkv, hd, geo.lpt, scale, cap, window, part_o, part_ml, n_splits, slopes
     int tt = (geo.cpl == 1 && geo.gt * 8 <= geo.lpt) ? 8 : ((geo.cpl <= 2 && geo.gt * 4 <= geo.lpt) ? 4 : 0);
     if (page_size <= 0 || (page_size & (page_size - 1)) || (ring > 0 && ring < 8 * 32)) tt = 0;   // the tiled kernel's address arithmetic
     bool launched = false;
@@ -484,7 +489,7 @@ static int decode_launch(const void* q, long long q_stride, const void* k_pool, 
         int combined = 0;
         const int rc = qnn_attn_decode_mma_split(q, q_stride, k_pool, v_pool, page_table, max_pages, page_size, ring,
                                                  slots, slot_len, B, nq, nkv, hd, scale, cap, window, part_o, part_ml,
-                                                 n_splits, out, out_stride, &combined, st);
+                                                 n_splits, out, out_stride, &combined, slopes, st);
         if (rc == 0 && combined) return 0;            // merged inside the kernel's clusters
         if (rc == 0) launched = true;
         else if (rc != QNN_ERR_UNSUPPORTED) return rc;
@@ -542,12 +547,12 @@ QNN_API int qnn_attn_decode(const void* q, long long q_stride, int dtype, const 
                             const int* page_table, int max_pages, int page_size, int ring, const int* slots,
                             const int* slot_len, int B, int nq, int nkv, int hd, float scale, float cap, int window,
                             float* part_o, float* part_ml, int n_splits, void* out, long long out_stride,
-                            cudaStream_t st) {
+                            const float* slopes, cudaStream_t st) {
     if (B <= 0) return 0;
     if (n_splits < 1 || n_splits > 65535 || B > 65535) return QNN_ERR_ARGUMENT;
     if (dtype == QNN_DT_BF16)
         return decode_launch<bf16>(q, q_stride, k_pool, v_pool, page_table, max_pages, page_size, ring, slots, slot_len,
-                                   B, nq, nkv, hd, scale, cap, window, part_o, part_ml, n_splits, out, out_stride, st);
+                                   B, nq, nkv, hd, scale, cap, window, part_o, part_ml, n_splits, out, out_stride, slopes, st);
     return decode_launch<float>(q, q_stride, k_pool, v_pool, page_table, max_pages, page_size, ring, slots, slot_len, B,
-                                nq, nkv, hd, scale, cap, window, part_o, part_ml, n_splits, out, out_stride, st);
+                                nq, nkv, hd, scale, cap, window, part_o, part_ml, n_splits, out, out_stride, slopes, st);
 }

@@ -122,7 +122,8 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
                        const bf16* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
                        int page_size, int ring, const int* __restrict__ slots, const int* __restrict__ slot_len,
                        int nq, int nkv, float scale, float cap, int window, float* __restrict__ part_o,
-                       float* __restrict__ part_ml, int n_splits, bf16* __restrict__ out, size_t out_stride) {
+                       float* __restrict__ part_ml, int n_splits, bf16* __restrict__ out, size_t out_stride,
+                       const float* __restrict__ slopes) {
     const bool CLUSTER = out != nullptr;         // launched as clusters of n_splits CTAs that merge their ranges
     constexpr int KSTEPS = HD / 16;              // k16 steps of S^T, and 16-row tiles of O^T
     constexpr int CH = HD / 8;                   // 16-byte chunks per row
@@ -146,9 +147,10 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
         for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
     float m0 = -CUDART_INF_F, m1 = -CUDART_INF_F, l0 = 0.f, l1 = 0.f;   // heads h0 + 2t and h0 + 2t + 1
 
-    int begin = 0, end = 0;
+    int begin = 0, end = 0, newest = 0;
     if (slot >= 0) {
         const int n = slot_len[slot];
+        newest = n - 1;
         const int kbeg = (window > 0 && n > window) ? n - window : 0;
         const int per = (n - kbeg + n_splits - 1) / n_splits;
         begin = kbeg + split * per;
@@ -212,6 +214,9 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
         for (int it = 0; it < MMA_STAGES - 1; ++it) fetch(it);
 
         const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+        // a bias by the distance to the newest position, a slope per query head (none without `slopes`)
+        const float slope0 = (slopes != nullptr && h0 + 2 * t < G) ? slopes[kh * G + h0 + 2 * t] : 0.f;
+        const float slope1 = (slopes != nullptr && h0 + 2 * t + 1 < G) ? slopes[kh * G + h0 + 2 * t + 1] : 0.f;
         for (int it = 0; it < my_tiles; ++it) {
             fetch(it + MMA_STAGES - 1);
             cp_async_wait<MMA_STAGES - 1>();
@@ -237,6 +242,7 @@ attn_decode_mma_kernel(const bf16* __restrict__ q, size_t q_stride, const bf16* 
             for (int j = 0; j < 4; ++j) {
                 float x = s[j] * scale;
                 if (cap > 0.f) x = cap * tanh_fast(fminf(fmaxf(x * inv_cap, -20.f), 20.f));
+                x -= ((j & 1) ? slope1 : slope0) * (float)(newest - (base + g + ((j >> 1) << 3)));
                 s[j] = ((j < 2) ? v_lo : v_hi) ? x : -CUDART_INF_F;
             }
             float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
@@ -436,7 +442,7 @@ template <int HD, int MMA_WARPS>
 int launch(const void* q, long long q_stride, const void* k_pool, const void* v_pool, const int* page_table,
            int max_pages, int page_size, int ring, const int* slots, const int* slot_len, int B, int nq, int nkv,
            float scale, float cap, int window, float* part_o, float* part_ml, int n_splits, void* out,
-           long long out_stride, int* combined, cudaStream_t st) {
+           long long out_stride, int* combined, const float* slopes, cudaStream_t st) {
     const size_t smem = smem_bytes<HD, MMA_WARPS, false>(max_pages);
     const size_t smem_c = smem_bytes<HD, MMA_WARPS, true>(max_pages);
     if (smem > 220 * 1024 || smem_c > 220 * 1024) return QNN_ERR_UNSUPPORTED;
@@ -473,14 +479,14 @@ int launch(const void* q, long long q_stride, const void* k_pool, const void* v_
         cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_mma_kernel<HD, MMA_WARPS, STC>, (const bf16*)q,
                                            (size_t)q_stride, (const bf16*)k_pool, (const bf16*)v_pool, page_table,
                                            max_pages, page_size, ring, slots, slot_len, nq, nkv, scale, cap, window,
-                                           part_o, part_ml, n_splits, (bf16*)out, (size_t)out_stride);
+                                           part_o, part_ml, n_splits, (bf16*)out, (size_t)out_stride, slopes);
         if (e != cudaSuccess) return (int)e;
         *combined = 1;
         return (int)cudaGetLastError();
     }
     qnn::launch_pdl(attn_decode_mma_kernel<HD, MMA_WARPS, ST>, dim3(grid), dim3(MMA_WARPS * 32), smem, st, (const bf16*)q, (size_t)q_stride, (const bf16*)k_pool, (const bf16*)v_pool,
                                              page_table, max_pages, page_size, ring, slots, slot_len, nq, nkv, scale,
-                                             cap, window, part_o, part_ml, n_splits, (bf16*)nullptr, (size_t)0);
+                                             cap, window, part_o, part_ml, n_splits, (bf16*)nullptr, (size_t)0, slopes);
     return (int)cudaGetLastError();
 }
 
@@ -498,13 +504,13 @@ extern "C" int qnn_attn_decode_mma_split(const void* q, long long q_stride, cons
                                          const int* slots, const int* slot_len, int B, int nq, int nkv, int hd,
                                          float scale, float cap, int window, float* part_o, float* part_ml,
                                          int n_splits, void* out, long long out_stride, int* combined,
-                                         cudaStream_t st) {
+                                         const float* slopes, cudaStream_t st) {
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
     if (page_size < TILE || (page_size & (page_size - 1))) return QNN_ERR_UNSUPPORTED;
     if (ring > 0 && (ring % page_size)) return QNN_ERR_UNSUPPORTED;
     if ((q_stride * 2) % 4 || ((uintptr_t)q & 3)) return QNN_ERR_UNSUPPORTED;
 #define QNN_MMA_ARGS q, q_stride, k_pool, v_pool, page_table, max_pages, page_size, ring, slots, slot_len, B, nq, nkv, \
-                     scale, cap, window, part_o, part_ml, n_splits, out, out_stride, combined, st
+                     scale, cap, window, part_o, part_ml, n_splits, out, out_stride, combined, slopes, st
     static int warps = 0;
     if (warps == 0) {
         const char* e = getenv("QNN_MMA_WARPS");

@@ -58,6 +58,7 @@ struct PackedKV {
 template <typename T, int CPL, int GT, typename KV>
 __device__ __forceinline__ void attend_range(const float (&q)[GT][CPL][Vec16<T>::N], const KV& kv, int begin, int end,
                                              int first, int stride, int LPT, int chunks, float cap,
+                                             const float (&slope)[GT], int qpos,
                                              float (&m)[GT], float (&l)[GT], float (&o)[GT][CPL][Vec16<T>::N]) {
     constexpr int VEC = Vec16<T>::N;
     const int lane = threadIdx.x & 31;
@@ -104,7 +105,8 @@ __device__ __forceinline__ void attend_range(const float (&q)[GT][CPL][Vec16<T>:
         if (valid) {
 #pragma unroll
             for (int g = 0; g < GT; ++g) {
-                const float sc = softcap(s[g], cap);
+                // a bias that grows with the distance to the query's position qpos, a slope per head (0: none)
+                const float sc = softcap(s[g], cap) - slope[g] * (float)(qpos - p);
                 const float mn = fmaxf(m[g], sc);
                 const float corr = fexp<T>(m[g] - mn);  // m = -inf on the first key gives 0
                 const float w = fexp<T>(sc - mn);
@@ -117,6 +119,13 @@ __device__ __forceinline__ void attend_range(const float (&q)[GT][CPL][Vec16<T>:
             }
         }
     }
+}
+
+// The distance slopes of the GT query heads of a head tile (slopes: one per query head, or null for none).
+template <int GT>
+__device__ __forceinline__ void load_slopes(const float* __restrict__ slopes, int head0, int G, int gt0, float (&sl)[GT]) {
+#pragma unroll
+    for (int g = 0; g < GT; ++g) sl[g] = (slopes != nullptr && gt0 + g < G) ? slopes[head0 + gt0 + g] : 0.f;
 }
 
 // Merge the states of the 32/LPT lane groups of a warp; afterwards every lane holds the

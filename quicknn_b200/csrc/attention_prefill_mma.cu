@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32, (BM + 4 * BN) * HD * 2 <= 112 *
 attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                         size_t row_stride, bf16* __restrict__ out, size_t out_stride,
                         const int* __restrict__ seq_row0, const int* __restrict__ seq_len, int nq, int nkv, float scale,
-                        float cap, int window) {
+                        float cap, int window, const float* __restrict__ slopes) {
     pdl_wait();
     constexpr int KSTEPS = HD / 16, CH = HD / 8, ROWB = HD * 2, NDT = HD / 8;
     constexpr int TILEB = BN * ROWB;
@@ -111,6 +111,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, 
         for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
     float m_[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_[2] = {0.f, 0.f};
     const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+    const float slope = slopes != nullptr ? slopes[h] : 0.f;     // a bias by the distance between query and key
     const int qrow_lo = r0 + warp * 16 + g;            // this lane's rows: qrow_lo and qrow_lo + 8
 
     for (int jt = jt_first, n = 0; jt <= jt_last; ++jt, ++n) {
@@ -156,6 +157,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, 
                 const int row = qrow_lo + ((j >> 1) << 3);
                 float x = s[nt][j] * scale;
                 if (cap > 0.f) x = cap * tanh_fast(fminf(fmaxf(x * inv_cap, -20.f), 20.f));
+                x -= slope * (float)(row - col);
                 const bool seen = col <= row && col < len && (window <= 0 || col > row - window);
                 x = seen ? x : -CUDART_INF_F;
                 s[nt][j] = x;
@@ -228,7 +230,7 @@ attn_prefill_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, 
 template <int HD, int BN>
 int launch(const void* q, const void* k, const void* v, long long row_stride, void* out, long long out_stride,
            const int* seq_row0, const int* seq_len, int B, int max_len, int nq, int nkv, float scale, float cap,
-           int window, cudaStream_t st) {
+           int window, const float* slopes, cudaStream_t st) {
     auto kern = attn_prefill_mma_kernel<HD, BN>;
     const size_t smem = (size_t)(BM + 4 * BN) * HD * 2;
     static bool configured = false;
@@ -240,7 +242,7 @@ int launch(const void* q, const void* k, const void* v, long long row_stride, vo
     dim3 grid(nq, B, (max_len + BM - 1) / BM);
     qnn::launch_pdl(kern, dim3(grid), dim3(PF_WARPS * 32), smem, st, (const bf16*)q, (const bf16*)k, (const bf16*)v, (size_t)row_stride,
                                             (bf16*)out, (size_t)out_stride, seq_row0, seq_len, nq, nkv, scale, cap,
-                                            window);
+                                            window, slopes);
     return (int)cudaGetLastError();
 }
 
@@ -251,7 +253,8 @@ int launch(const void* q, const void* k, const void* v, long long row_stride, vo
 // lengths.  Returns QNN_ERR_UNSUPPORTED for head sizes other than 64, 128, 256.
 QNN_API int qnn_attn_prefill_mma(const void* q, const void* k, const void* v, long long row_stride, void* out,
                                  long long out_stride, const int* seq_row0, const int* seq_len, int B, int max_len,
-                                 int nq, int nkv, int hd, float scale, float cap, int window, cudaStream_t st) {
+                                 int nq, int nkv, int hd, float scale, float cap, int window, const float* slopes,
+                                 cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return 0;
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
     if (B > 65535 || (max_len + BM - 1) / BM > 65535) return QNN_ERR_UNSUPPORTED;
@@ -259,10 +262,10 @@ QNN_API int qnn_attn_prefill_mma(const void* q, const void* k, const void* v, lo
         (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) || ((uintptr_t)out & 3))
         return QNN_ERR_ARGUMENT;
     switch (hd) {
-        case 64: return launch<64, 64>(q, k, v, row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, st);
-        case 128: return launch<128, 64>(q, k, v, row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, st);
+        case 64: return launch<64, 64>(q, k, v, row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, slopes, st);
+        case 128: return launch<128, 64>(q, k, v, row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, slopes, st);
         case 256: return launch<256, 32>(q, k, v,      // 32-key tiles: 96 KB of shared memory, two CTAs per SM
-                                          row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, st);
+                                          row_stride, out, out_stride, seq_row0, seq_len, B, max_len, nq, nkv, scale, cap, window, slopes, st);
         default: return QNN_ERR_UNSUPPORTED;
     }
 }

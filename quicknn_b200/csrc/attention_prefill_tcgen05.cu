@@ -126,7 +126,8 @@ __global__ void __launch_bounds__(THREADS)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             bf16* __restrict__ out, size_t out_stride, const int* __restrict__ seq_row0,
                             const int* __restrict__ seq_len, const int* __restrict__ seq_q0, int nq, int nkv,
-                            float scale, float cap, int window, int* __restrict__ status, int split_levels) {
+                            float scale, float cap, int window, int* __restrict__ status, int split_levels,
+                            const float* __restrict__ slopes) {
     constexpr int KS = k_stages(HD), VS = v_stages(HD);
     constexpr int Q_BYTES = BM * HD * 2;                             // HD / 64 blocks of [128 x 64]
     constexpr int KP_BYTES = 2 * BN * HD * 2;                        // a pair of key tiles: HD / 64 blocks of [128 x 64]
@@ -225,6 +226,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const float LOG2E = 1.4426950408889634f;
     const float k1 = cap > 0.f ? scale / cap : scale;
     const float k2 = (cap > 0.f ? cap : 1.f) * LOG2E;
+    // a bias by the distance between query and key, a slope per head, in the unit of the tracked maximum (the
+    // running-maximum form only: the launcher never pairs slopes with the fixed reference)
+    const float slope_u = slopes != nullptr ? slopes[h] / (cap > 0.f ? cap : 1.f) : 0.f;
     const float step = RESCALE_STEP / (cap > 0.f ? cap : 1.f);   // a growth of the maximum by 8 in the exponent
     float m_used = 0.f, l_sum = 0.f;                      // reference maximum of the exponentials, their sum
     bool alive = true;
@@ -426,7 +430,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (interior) {
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
-                    const float x = cap > 0.f ? tanh_fast(s[c] * k1) : s[c] * k1;
+                    float x = cap > 0.f ? tanh_fast(s[c] * k1) : s[c] * k1;
+                    x = fmaf(slope_u, (float)(col0 + c - row), x);
                     s[c] = x;
                     mx4[c & 3] = fmaxf(mx4[c & 3], x);
                 }
@@ -434,6 +439,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
                     float x = cap > 0.f ? tanh_fast(s[c] * k1) : s[c] * k1;
+                    x = fmaf(slope_u, (float)(col0 + c - row), x);
                     const bool seen = (unsigned)(col0 + c - key_lo) <= key_span;      // key_lo <= column <= key_hi
                     x = seen ? x : -CUDART_INF_F;
                     s[c] = x;
@@ -664,7 +670,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 template <int HD, bool FIXED>
 int launch_attn(const void* qkv, long long total_rows, void* out, long long out_stride, const int* seq_row0,
                 const int* seq_len, const int* seq_q0, int B, int max_len, int nq, int nkv, float scale, float cap,
-                int window, int* status, cudaStream_t st) {
+                int window, int* status, const float* slopes, cudaStream_t st) {
     const long long width = (long long)(nq + 2 * nkv) * HD;
     CUtensorMap map_q, map_kv;
     int rc = make_map(&map_q, qkv, total_rows, width, BM);
@@ -737,7 +743,7 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
         cfg.numAttrs = pdl ? 1 : 0;
     }
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_q, map_kv, (bf16*)out, (size_t)out_stride, seq_row0, seq_len, seq_q0, nq,
-                                       nkv, scale, cap, window, status, split);
+                                       nkv, scale, cap, window, status, split, slopes);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -754,13 +760,13 @@ int launch_attn(const void* qkv, long long total_rows, void* out, long long out_
 QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void* out, long long out_stride,
                                      const int* seq_row0, const int* seq_len, const int* seq_q0, int B, int max_len,
                                      int nq, int nkv, int hd, float scale, float cap, int window, int* status,
-                                     cudaStream_t st) {
+                                     const float* slopes, cudaStream_t st) {
     if (B <= 0 || max_len <= 0) return 0;
     if (hd != 64 && hd != 128 && hd != 256) return QNN_ERR_UNSUPPORTED;
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
     if (B > 65535 || nq > 32767 || (max_len + BM - 1) / BM > 65535) return QNN_ERR_UNSUPPORTED;
     if (((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) || (out_stride * 2) % 16) return QNN_ERR_UNSUPPORTED;
-#define QNN_ATTN_ARGS qkv, total_rows, out, out_stride, seq_row0, seq_len, seq_q0, B, max_len, nq, nkv, scale, cap, window, status, st
+#define QNN_ATTN_ARGS qkv, total_rows, out, out_stride, seq_row0, seq_len, seq_q0, B, max_len, nq, nkv, scale, cap, window, status, slopes, st
     // With a softcap up to 70 the exponent cap * log2(e) stays below 101, so that neither exp(score) nor a row's
     // sum over a million keys leaves float32: the fixed-reference softmax with both groups of warps.  QNN_ATTN_FIXED=0
     // keeps the running maximum (for comparisons).
@@ -769,7 +775,7 @@ QNN_API int qnn_attn_prefill_tcgen05(const void* qkv, long long total_rows, void
         const char* e = getenv("QNN_ATTN_FIXED");
         fixed_ok = (e && e[0] == '0') ? 0 : 1;
     }
-    const bool fixed = fixed_ok && cap > 0.f && cap <= 70.f;
+    const bool fixed = fixed_ok && cap > 0.f && cap <= 70.f && slopes == nullptr;
     switch (hd) {
         case 64: return fixed ? launch_attn<64, true>(QNN_ATTN_ARGS) : launch_attn<64, false>(QNN_ATTN_ARGS);
         case 128: return fixed ? launch_attn<128, true>(QNN_ATTN_ARGS) : launch_attn<128, false>(QNN_ATTN_ARGS);

@@ -46,7 +46,7 @@ attn_prefill_generic_kernel(const T* __restrict__ q, size_t q_stride, const T* _
                             size_t row_stride, T* __restrict__ out, size_t out_stride, const int* __restrict__ tok_pos,
                             const int* __restrict__ tok_row0, int n_tokens, int nq, int nkv, int hd, int LPT,
                             float scale, float cap, int window, const int* __restrict__ page_table, int max_pages,
-                            int page_size, int ring) {
+                            int page_size, int ring, const float* __restrict__ slopes) {
     pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     const int warp = threadIdx.x >> 5;
@@ -72,14 +72,15 @@ attn_prefill_generic_kernel(const T* __restrict__ q, size_t q_stride, const T* _
         const int p = tok_pos[t];
         const int end = p + 1;
         const int begin = (window > 0 && end > window) ? end - window : 0;
-        float qr[GT][CPL][VEC];
+        float qr[GT][CPL][VEC], sl[GT];
         load_query<T, CPL, GT>(q + (size_t)t * q_stride + (size_t)kh * G * hd, hd, G, gt0, LPT, chunks, scale, qr);
+        load_slopes<GT>(slopes, kh * G, G, gt0, sl);
         if (PAGED) {
             PagedKV<T> kv{k, v, page_table + (size_t)row0 * max_pages, page_size, nkv, hd, ring, kh};
-            attend_range<T, CPL, GT>(qr, kv, begin, end, 0, TPW, LPT, chunks, cap, m, l, o);
+            attend_range<T, CPL, GT>(qr, kv, begin, end, 0, TPW, LPT, chunks, cap, sl, p, m, l, o);
         } else {
             PackedKV<T> kv{k + (size_t)kh * hd, v + (size_t)kh * hd, row_stride, row0};
-            attend_range<T, CPL, GT>(qr, kv, begin, end, 0, TPW, LPT, chunks, cap, m, l, o);
+            attend_range<T, CPL, GT>(qr, kv, begin, end, 0, TPW, LPT, chunks, cap, sl, p, m, l, o);
         }
     }
     merge_groups<CPL, GT, VEC>(LPT, m, l, o);
@@ -100,7 +101,8 @@ attn_extend_generic_kernel(const T* __restrict__ q, size_t q_stride, const T* __
                            T* __restrict__ out, size_t out_stride, const int* __restrict__ tok_pos,
                            const int* __restrict__ tok_row0, const int* __restrict__ tok_slot, int n_tokens, int nq,
                            int nkv, int hd, int LPT, float scale, float cap, int window,
-                           const int* __restrict__ page_table, int max_pages, int page_size, int ring) {
+                           const int* __restrict__ page_table, int max_pages, int page_size, int ring,
+                           const float* __restrict__ slopes) {
     pdl_wait();
     constexpr int VEC = Vec16<T>::N;
     const int warp = threadIdx.x >> 5;
@@ -127,14 +129,15 @@ attn_extend_generic_kernel(const T* __restrict__ q, size_t q_stride, const T* __
         const int first = p - (t - row0);                 // position of the sequence's first token of this step
         const int end = p + 1;
         const int begin = (window > 0 && end > window) ? end - window : 0;
-        float qr[GT][CPL][VEC];
+        float qr[GT][CPL][VEC], sl[GT];
         load_query<T, CPL, GT>(q + (size_t)t * q_stride + (size_t)kh * G * hd, hd, G, gt0, LPT, chunks, scale, qr);
+        load_slopes<GT>(slopes, kh * G, G, gt0, sl);
         if (begin < first) {
             PagedKV<T> kv{k_pool, v_pool, page_table + (size_t)slot * max_pages, page_size, nkv, hd, ring, kh};
-            attend_range<T, CPL, GT>(qr, kv, begin, first, 0, TPW, LPT, chunks, cap, m, l, o);
+            attend_range<T, CPL, GT>(qr, kv, begin, first, 0, TPW, LPT, chunks, cap, sl, p, m, l, o);
         }
         PackedKV<T> kv{k + (size_t)kh * hd, v + (size_t)kh * hd, row_stride, row0 - first};
-        attend_range<T, CPL, GT>(qr, kv, begin > first ? begin : first, end, 0, TPW, LPT, chunks, cap, m, l, o);
+        attend_range<T, CPL, GT>(qr, kv, begin > first ? begin : first, end, 0, TPW, LPT, chunks, cap, sl, p, m, l, o);
     }
     merge_groups<CPL, GT, VEC>(LPT, m, l, o);
     store_rows<T, CPL, GT>(out + (size_t)t * out_stride, kh, G, gt0, hd, LPT, chunks, l, o);
@@ -146,7 +149,7 @@ template <typename T>
 static int prefill_launch(const void* q, long long q_stride, const void* k, const void* v, long long row_stride,
                           void* out, long long out_stride, const int* tok_pos, const int* tok_row0, int n_tokens,
                           int nq, int nkv, int hd, float scale, float cap, int window, const int* page_table,
-                          int max_pages, int page_size, int ring, bool paged, cudaStream_t st) {
+                          int max_pages, int page_size, int ring, bool paged, const float* slopes, cudaStream_t st) {
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
     const Geometry geo = geometry<T>(hd, nq / nkv);
     if (!geo.ok) return QNN_ERR_UNSUPPORTED;
@@ -160,12 +163,12 @@ static int prefill_launch(const void* q, long long q_stride, const void* k, cons
             qnn::launch_pdl(attn_prefill_generic_kernel<T, CPL, GT, true>, dim3(grid), dim3(PRE_WARPS * 32), 0, st, 
                 (const T*)q, (size_t)q_stride, (const T*)k, (const T*)v, (size_t)row_stride, (T*)out,
                 (size_t)out_stride, tok_pos, tok_row0, n_tokens, nq, nkv, hd, geo.lpt, scale, cap, window, page_table,
-                max_pages, page_size, ring);
+                max_pages, page_size, ring, slopes);
         else
             qnn::launch_pdl(attn_prefill_generic_kernel<T, CPL, GT, false>, dim3(grid), dim3(PRE_WARPS * 32), 0, st, 
                 (const T*)q, (size_t)q_stride, (const T*)k, (const T*)v, (size_t)row_stride, (T*)out,
                 (size_t)out_stride, tok_pos, tok_row0, n_tokens, nq, nkv, hd, geo.lpt, scale, cap, window, page_table,
-                max_pages, page_size, ring);
+                max_pages, page_size, ring, slopes);
     })
     QNN_LAUNCH_CHECK();
 }
@@ -175,13 +178,13 @@ static int prefill_launch(const void* q, long long q_stride, const void* k, cons
 QNN_API int qnn_attn_prefill_generic(const void* q, const void* k, const void* v, long long row_stride, int dtype,
                                      void* out, long long out_stride, const int* tok_pos, const int* tok_row0,
                                      int n_tokens, int nq, int nkv, int hd, float scale, float cap, int window,
-                                     cudaStream_t st) {
+                                     const float* slopes, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (dtype == QNN_DT_BF16)
         return prefill_launch<bf16>(q, row_stride, k, v, row_stride, out, out_stride, tok_pos, tok_row0, n_tokens, nq,
-                                    nkv, hd, scale, cap, window, nullptr, 0, 1, 0, false, st);
+                                    nkv, hd, scale, cap, window, nullptr, 0, 1, 0, false, slopes, st);
     return prefill_launch<float>(q, row_stride, k, v, row_stride, out, out_stride, tok_pos, tok_row0, n_tokens, nq, nkv,
-                                 hd, scale, cap, window, nullptr, 0, 1, 0, false, st);
+                                 hd, scale, cap, window, nullptr, 0, 1, 0, false, slopes, st);
 }
 
 // Cached keys before this step's tokens, this step's own rows from there on (see
@@ -190,7 +193,8 @@ template <typename T>
 static int extend_launch(const void* q, const void* k, const void* v, long long row_stride, const void* k_pool,
                          const void* v_pool, const int* page_table, int max_pages, int page_size, int ring, void* out,
                          long long out_stride, const int* tok_pos, const int* tok_row0, const int* tok_slot, int n_tokens,
-                         int nq, int nkv, int hd, float scale, float cap, int window, cudaStream_t st) {
+                         int nq, int nkv, int hd, float scale, float cap, int window, const float* slopes,
+                         cudaStream_t st) {
     if (nkv <= 0 || nq % nkv) return QNN_ERR_ARGUMENT;
     const Geometry geo = geometry<T>(hd, nq / nkv);
     if (!geo.ok) return QNN_ERR_UNSUPPORTED;
@@ -203,7 +207,7 @@ static int extend_launch(const void* q, const void* k, const void* v, long long 
         qnn::launch_pdl(attn_extend_generic_kernel<T, CPL, GT>, dim3(grid), dim3(PRE_WARPS * 32), 0, st, (const T*)q,
                         (size_t)row_stride, (const T*)k, (const T*)v, (size_t)row_stride, (const T*)k_pool,
                         (const T*)v_pool, (T*)out, (size_t)out_stride, tok_pos, tok_row0, tok_slot, n_tokens, nq, nkv, hd,
-                        geo.lpt, scale, cap, window, page_table, max_pages, page_size, ring);
+                        geo.lpt, scale, cap, window, page_table, max_pages, page_size, ring, slopes);
     })
     QNN_LAUNCH_CHECK();
 }
@@ -212,13 +216,13 @@ QNN_API int qnn_attn_extend(const void* q, const void* k, const void* v, long lo
                             const void* k_pool, const void* v_pool, const int* page_table, int max_pages, int page_size,
                             int ring, void* out, long long out_stride, const int* tok_pos, const int* tok_row0,
                             const int* tok_slot, int n_tokens, int nq, int nkv, int hd, float scale, float cap,
-                            int window, cudaStream_t st) {
+                            int window, const float* slopes, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (dtype == QNN_DT_BF16)
         return extend_launch<bf16>(q, k, v, row_stride, k_pool, v_pool, page_table, max_pages, page_size, ring, out,
-                                   out_stride, tok_pos, tok_row0, tok_slot, n_tokens, nq, nkv, hd, scale, cap, window, st);
+                                   out_stride, tok_pos, tok_row0, tok_slot, n_tokens, nq, nkv, hd, scale, cap, window, slopes, st);
     return extend_launch<float>(q, k, v, row_stride, k_pool, v_pool, page_table, max_pages, page_size, ring, out,
-                                out_stride, tok_pos, tok_row0, tok_slot, n_tokens, nq, nkv, hd, scale, cap, window, st);
+                                out_stride, tok_pos, tok_row0, tok_slot, n_tokens, nq, nkv, hd, scale, cap, window, slopes, st);
 }
 
 // Several query rows per sequence against the paged cache: token t of the sequence in slot
@@ -227,13 +231,14 @@ QNN_API int qnn_attn_extend(const void* q, const void* k, const void* v, long lo
 QNN_API int qnn_attn_prefill_paged(const void* q, long long q_stride, int dtype, const void* k_pool, const void* v_pool,
                                    const int* page_table, int max_pages, int page_size, int ring, void* out,
                                    long long out_stride, const int* tok_pos, const int* tok_slot, int n_tokens, int nq,
-                                   int nkv, int hd, float scale, float cap, int window, cudaStream_t st) {
+                                   int nkv, int hd, float scale, float cap, int window, const float* slopes,
+                                   cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (dtype == QNN_DT_BF16)
         return prefill_launch<bf16>(q, q_stride, k_pool, v_pool, 0, out, out_stride, tok_pos, tok_slot, n_tokens, nq,
-                                    nkv, hd, scale, cap, window, page_table, max_pages, page_size, ring, true, st);
+                                    nkv, hd, scale, cap, window, page_table, max_pages, page_size, ring, true, slopes, st);
     return prefill_launch<float>(q, q_stride, k_pool, v_pool, 0, out, out_stride, tok_pos, tok_slot, n_tokens, nq, nkv,
-                                 hd, scale, cap, window, page_table, max_pages, page_size, ring, true, st);
+                                 hd, scale, cap, window, page_table, max_pages, page_size, ring, true, slopes, st);
 }
 
 // ---------------------------------------------------------------------------------

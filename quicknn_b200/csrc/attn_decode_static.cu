@@ -14,7 +14,7 @@ extern "C" int qnn_attn_decode(const void* q, long long q_stride, int dtype, con
                                const int* page_table, int max_pages, int page_size, int ring, const int* slots,
                                const int* slot_len, int B, int nq, int nkv, int hd, float scale, float cap,
                                int window, float* part_o, float* part_ml, int n_splits, void* out,
-                               long long out_stride, cudaStream_t st);
+                               long long out_stride, const float* slopes, cudaStream_t st);
 
 namespace {
 constexpr int kMaxDevices = 64;
@@ -65,5 +65,5 @@ QNN_API int qnn_attn_decode_static(const void* q, long long q_stride, int dtype,
     float* part_ml = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(base) + o_bytes);
     return qnn_attn_decode(q, q_stride, dtype, k_pool, v_pool, page_table, max_pages, page_size, ring, slots, slot_len,
                            B, n_heads, n_kv_heads, head_dim, scale, cap, window, part_o, part_ml, n_splits, out,
-                           out_stride, stream);
+                           out_stride, nullptr, stream);
 }

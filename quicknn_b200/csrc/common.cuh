@@ -144,6 +144,11 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 // argument (with the epilogue code "none"): act(x W^T).  Codes below it mean what they meant.
 #define QNN_ACT_ALONE 16
 __device__ __forceinline__ float relu2(float x) { const float r = fmaxf(x, 0.f); return x == x ? r * r : x; }
+// xIELU with its two constants already formed (ap = softplus(p), an = 1/2 + softplus(q)):
+// x > 0: ap x^2 + x / 2;  x <= 0: an (exp(x) - 1 - x) + x / 2.  Continuous with slope 1/2 at 0.
+__device__ __forceinline__ float xielu(float x, float ap, float an) {
+    return x > 0.f ? fmaf(ap * x, x, 0.5f * x) : fmaf(an, expm1f(x) - x, 0.5f * x);
+}
 __device__ __forceinline__ float activate(float x, int act) {
     return act == QNN_ACT_SILU ? silu(x) : (act == QNN_ACT_RELU2 ? relu2(x) : gelu_tanh(x));
 }

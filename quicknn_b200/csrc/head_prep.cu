@@ -3,6 +3,8 @@
 //   1. a bias over the packed row (optional);
 //   2. an RMS norm per head over the first `norm_dim` columns of every query and key head, with a weight per column
 //      that all heads share (optional; the heads may be carried wider than norm_dim, with zero columns behind);
+//      or, with `norm_whole`, one RMS norm over all query heads together and one over all key heads together (the
+//      first norm_dim columns of each head count), with a weight per head and column;
 //   3. a rotation of the first `rot` columns of every query and key head by position * inv_freq[j], the pair of
 //      frequency j being columns (j, j + rot/2) (half-split) or (2j, 2j + 1) (interleaved);
 //   4. the row written back in place, or to another buffer of another element type (float32 rows for a recurrence
@@ -25,8 +27,8 @@ __global__ void head_prep_kernel(const T* src, long long lds, void* dst, int dst
                                  const void* __restrict__ wk, int w_dt, float eps, const float* __restrict__ inv_freq,
                                  const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, T* __restrict__ k_pool,
                                  T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages, int page_size,
-                                 int ring, const int* __restrict__ slot_len, int write_cache) {
-    extern __shared__ float sm[];                   // [rot/2] (cos, sin) pairs, then a head of hd floats per warp
+                                 int ring, const int* __restrict__ slot_len, int write_cache, int norm_whole) {
+    extern __shared__ float sm[];                   // [rot/2] (cos, sin) pairs, a head of hd floats per warp, [nq + nk] sums
     pdl_wait();
     const int t = blockIdx.x;
     const int pos = tok_pos != nullptr ? tok_pos[t] : 0;
@@ -54,6 +56,27 @@ __global__ void head_prep_kernel(const T* src, long long lds, void* dst, int dst
     const size_t out_row = (size_t)t * ldd;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
     float* mine = heads + (size_t)warp * hd;
+    float inv_q = 0.f, inv_k = 0.f;
+    if (norm_whole) {
+        // every head's sum of squares first, then the heads in order: the same sum whatever the block's size
+        float* sums = heads + (size_t)nwarp * hd;
+        for (int h = warp; h < nq + nk; h += nwarp) {
+            float ss = 0.f;
+            for (int c = lane; c < norm_dim; c += 32) {
+                float v = to_f(row[(size_t)h * hd + c]);
+                if (bias != nullptr) v += load_as_f(bias, b_dt, (size_t)h * hd + c);
+                ss += v * v;
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) sums[h] = ss;
+        }
+        __syncthreads();
+        float sq = 0.f, sk = 0.f;
+        for (int h = 0; h < nq; ++h) sq += sums[h];
+        for (int h = nq; h < nq + nk; ++h) sk += sums[h];
+        inv_q = rsqrtf(sq / (float)(nq > 0 ? nq * norm_dim : 1) + eps);
+        inv_k = rsqrtf(sk / (float)(nk > 0 ? nk * norm_dim : 1) + eps);
+    }
     for (int h = warp; h < nq + nk; h += nwarp) {
         const bool is_k = h >= nq;
         const size_t c0 = (size_t)h * hd;
@@ -67,8 +90,9 @@ __global__ void head_prep_kernel(const T* src, long long lds, void* dst, int dst
         const void* w = is_k ? wk : wq;
         if (w != nullptr) {
             ss = warp_sum(ss);
-            const float inv = rsqrtf(ss / (float)norm_dim + eps);
-            for (int c = lane; c < norm_dim; c += 32) mine[c] = mine[c] * inv * load_as_f(w, w_dt, c);
+            const float inv = norm_whole ? (is_k ? inv_k : inv_q) : rsqrtf(ss / (float)norm_dim + eps);
+            const size_t w0 = norm_whole ? (size_t)(is_k ? h - nq : h) * norm_dim : 0;
+            for (int c = lane; c < norm_dim; c += 32) mine[c] = mine[c] * inv * load_as_f(w, w_dt, w0 + c);
         }
         __syncwarp();
         for (int j = lane; j < rh; j += 32) {
@@ -109,8 +133,8 @@ __global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, v
                                      const void* __restrict__ wk, int w_dt, float eps, const float* __restrict__ inv_freq,
                                      const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, void* k_pool,
                                      void* v_pool, const int* __restrict__ page_table, int max_pages, int page_size,
-                                     int ring, const int* __restrict__ slot_len, int write_cache) {
-    extern __shared__ float sm[];                   // [rot/2] (cos, sin) pairs
+                                     int ring, const int* __restrict__ slot_len, int write_cache, int norm_whole) {
+    extern __shared__ float sm[];                   // [rot/2] (cos, sin) pairs, then [nq + nk] sums
     pdl_wait();
     const int t = blockIdx.x;
     const int pos = tok_pos != nullptr ? tok_pos[t] : 0;
@@ -136,6 +160,34 @@ __global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, v
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
     const int col = lane * 8, shift = rh / 8;
     const bool active = col < hd;
+    float inv_q = 0.f, inv_k = 0.f;
+    if (norm_whole) {
+        float* sums = sm + 2 * rh;
+        for (int h = warp; h < nq + nk; h += nwarp) {
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (active) {
+                load8_as_f(src, s_dt, in_row + (size_t)h * hd + col, v);
+                if (bias != nullptr) {
+                    float b[8];
+                    load8_as_f(bias, b_dt, (size_t)h * hd + col, b);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] += b[e];
+                }
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (col + e < norm_dim) ss += v[e] * v[e];
+            ss = warp_sum(ss);
+            if (lane == 0) sums[h] = ss;
+        }
+        __syncthreads();
+        float sq = 0.f, sk = 0.f;
+        for (int h = 0; h < nq; ++h) sq += sums[h];
+        for (int h = nq; h < nq + nk; ++h) sk += sums[h];
+        inv_q = rsqrtf(sq / (float)(nq > 0 ? nq * norm_dim : 1) + eps);
+        inv_k = rsqrtf(sk / (float)(nk > 0 ? nk * norm_dim : 1) + eps);
+    }
     for (int h = warp; h < nq + nk; h += nwarp) {
         const bool is_k = h >= nq;
         const size_t c0 = (size_t)h * hd;
@@ -156,10 +208,11 @@ __global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, v
             for (int e = 0; e < 8; ++e)
                 if (col + e < norm_dim) ss += v[e] * v[e];
             ss = warp_sum(ss);
-            const float inv = rsqrtf(ss / (float)norm_dim + eps);
+            const float inv = norm_whole ? (is_k ? inv_k : inv_q) : rsqrtf(ss / (float)norm_dim + eps);
+            const size_t w0 = norm_whole ? (size_t)(is_k ? h - nq : h) * norm_dim : 0;
 #pragma unroll
             for (int e = 0; e < 8; ++e)
-                if (col + e < norm_dim) v[e] = v[e] * inv * load_as_f(w, w_dt, col + e);
+                if (col + e < norm_dim) v[e] = v[e] * inv * load_as_f(w, w_dt, w0 + col + e);
         }
         if (rot > 0) {
             if (interleaved) {
@@ -215,17 +268,19 @@ __global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, v
 
 // src: [T, lds] rows of `dtype` holding nq query heads, nk key heads (hd columns each) and nv value columns, in that
 // order; dst: the same layout with row pitch ldd in `dst_dt` (may be src itself).  bias: over the packed row, or null.
-// wq / wk: norm weights [norm_dim] of `w_dt`, or null.  inv_freq: [rot/2] float32.  The cache arguments are those of
+// wq / wk: norm weights [norm_dim] of `w_dt` (with norm_whole: [nq * norm_dim] and [nk * norm_dim]), or null.  inv_freq: [rot/2] float32.  The cache arguments are those of
 // qnn_rope_cache_write; with write_cache, nv must be nk * hd (or 0 with v_pool null) and dst_dt the pools' type.
 QNN_API int qnn_head_prep(const void* src, int dtype, long long lds, void* dst, int dst_dt, long long ldd, int T, int nq,
                           int nk, int nv, int hd, int norm_dim, int rot, int interleaved, const void* bias, int b_dt,
                           const void* wq, const void* wk, int w_dt, float eps, const float* inv_freq, const int* tok_pos,
                           const int* tok_slot, void* k_pool, void* v_pool, const int* page_table, int max_pages,
-                          int page_size, int ring, const int* slot_len, int write_cache, cudaStream_t st) {
+                          int page_size, int ring, const int* slot_len, int write_cache, int norm_whole,
+                          cudaStream_t st) {
     if (T <= 0) return 0;
     if (nq < 0 || nk < 0 || nv < 0 || hd <= 0 || rot % 2 || rot < 0 || rot > hd || norm_dim < 0 || norm_dim > hd)
         return QNN_ERR_ARGUMENT;
     if ((wq != nullptr || wk != nullptr) && norm_dim == 0) return QNN_ERR_ARGUMENT;
+    if (norm_whole && ((nq > 0 && wq == nullptr) || (nk > 0 && wk == nullptr))) return QNN_ERR_ARGUMENT;
     if (rot > 0 && (inv_freq == nullptr || tok_pos == nullptr)) return QNN_ERR_ARGUMENT;
     if (write_cache && (tok_slot == nullptr || k_pool == nullptr || page_table == nullptr || slot_len == nullptr ||
                         (v_pool != nullptr && nv != nk * hd)))
@@ -240,20 +295,21 @@ QNN_API int qnn_head_prep(const void* src, int dtype, long long lds, void* dst, 
                          (ldd * ed) % 16 == 0 && ((uintptr_t)bias % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) &&
                          ((uintptr_t)v_pool % 16 == 0);
     if (aligned && hd % 8 == 0 && hd <= 256 && nv % 8 == 0 && (interleaved ? rot % 2 == 0 : rot % 16 == 0)) {
-        launch_pdl(head_prep_vec_kernel, dim3(T), dim3(warps * 32), (size_t)rot * sizeof(float), st, src, dtype, lds, dst,
-                   dst_dt, ldd, nq, nk, nv, hd, norm_dim, rot, interleaved, bias, b_dt, wq, wk, w_dt, eps, inv_freq, tok_pos,
-                   tok_slot, k_pool, v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache);
+        launch_pdl(head_prep_vec_kernel, dim3(T), dim3(warps * 32), ((size_t)rot + heads) * sizeof(float), st, src, dtype, lds,
+                   dst, dst_dt, ldd, nq, nk, nv, hd, norm_dim, rot, interleaved, bias, b_dt, wq, wk, w_dt, eps, inv_freq,
+                   tok_pos, tok_slot, k_pool, v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache,
+                   norm_whole);
         QNN_LAUNCH_CHECK();
     }
-    const size_t smem = ((size_t)rot + (size_t)warps * hd) * sizeof(float);
+    const size_t smem = ((size_t)rot + (size_t)warps * hd + heads) * sizeof(float);
     if (smem > 48 * 1024) return QNN_ERR_UNSUPPORTED;
     if (dtype == QNN_DT_BF16)
         launch_pdl(head_prep_kernel<bf16>, dim3(T), dim3(warps * 32), smem, st, (const bf16*)src, lds, dst, dst_dt, ldd, nq, nk,
                    nv, hd, norm_dim, rot, interleaved, bias, b_dt, wq, wk, w_dt, eps, inv_freq, tok_pos, tok_slot,
-                   (bf16*)k_pool, (bf16*)v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache);
+                   (bf16*)k_pool, (bf16*)v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache, norm_whole);
     else
         launch_pdl(head_prep_kernel<float>, dim3(T), dim3(warps * 32), smem, st, (const float*)src, lds, dst, dst_dt, ldd, nq,
                    nk, nv, hd, norm_dim, rot, interleaved, bias, b_dt, wq, wk, w_dt, eps, inv_freq, tok_pos, tok_slot,
-                   (float*)k_pool, (float*)v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache);
+                   (float*)k_pool, (float*)v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache, norm_whole);
     QNN_LAUNCH_CHECK();
 }

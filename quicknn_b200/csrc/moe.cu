@@ -36,8 +36,9 @@ constexpr int MAX_TOP = 16;
 
 template <typename TX, typename TW>
 __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict__ wr, int T, int W, int E, int top,
-                                 int score_fn, int renorm, int* __restrict__ sel_e, float* __restrict__ sel_w) {
-    extern __shared__ float sc[];                       // [E]
+                                 int score_fn, int renorm, const float* __restrict__ correction, float out_scale,
+                                 int* __restrict__ sel_e, float* __restrict__ sel_w) {
+    extern __shared__ float sc[];                       // [E] logits (then scores), [E] what the experts are ranked by
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -78,12 +79,24 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict_
         for (int e = lane; e < E; e += 32) sum += expf(s[e] - m);
         sum = warp_sum(sum);
     }
+    // With a correction the experts are ranked by score + correction[e] and weighted by the score alone, so every
+    // expert's score is formed first.
+    float* rank = s;
+    if (correction != nullptr) {
+        rank = s + E;
+        for (int e = lane; e < E; e += 32) {
+            const float v = score_fn == QNN_MOE_SCORE_SOFTMAX ? expf(s[e] - m) / sum : 1.f / (1.f + expf(-s[e]));
+            s[e] = v;
+            rank[e] = v + correction[e];
+        }
+        __syncwarp();
+    }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int arg = 0x7fffffff;
         for (int e = lane; e < E; e += 32) {
-            const float v = s[e];
+            const float v = rank[e];
             if (v > best) { best = v; arg = e; }          // ascending e: the first of equals stays
         }
 #pragma unroll
@@ -93,23 +106,30 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict_
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
         if (arg == 0x7fffffff) arg = 0;                    // logits that are all NaN: any expert, the model's logits will show it
-        best = score_fn == QNN_MOE_SCORE_SOFTMAX ? expf(best - m) / sum : 1.f / (1.f + expf(-best));
+        if (correction != nullptr) best = s[arg];
+        else best = score_fn == QNN_MOE_SCORE_SOFTMAX ? expf(best - m) / sum : 1.f / (1.f + expf(-best));
         total += best;
+        __syncwarp();
         if (lane == 0) {
             sel_e[(size_t)t * top + k] = arg;
             sel_w[(size_t)t * top + k] = best;
-            s[arg] = -INFINITY;
+            rank[arg] = -INFINITY;
         }
         __syncwarp();
     }
-    if (renorm && lane == 0)
-        for (int k = 0; k < top; ++k) sel_w[(size_t)t * top + k] /= total;
+    if (lane == 0 && (renorm || out_scale != 1.f))
+        for (int k = 0; k < top; ++k) {
+            float w = sel_w[(size_t)t * top + k];
+            if (renorm) w /= total;
+            sel_w[(size_t)t * top + k] = w * out_scale;
+        }
 }
 
 // ---- grouping ----------------------------------------------------------------------------------------
 
 // offsets: [E + 1]; perm: [n] sorted place -> entry (row * top + k); tiles: [max_tiles][2] (expert, first sorted
-// place); n_tiles: [1].  Which of an expert's rows comes first varies from run to run; no result depends on it.
+// place); n_tiles: [1].  An entry whose expert id is not in [0, E) belongs to no expert (an identity expert, which
+// the combine step serves): it gets no place, and the places behind offsets[E] name entry 0.  Which of an expert's rows comes first varies from run to run; no result depends on it.
 __global__ void moe_plan_kernel(const int* __restrict__ sel_e, int n, int E, int tile_rows, int* __restrict__ offsets,
                                 int* __restrict__ perm, int* __restrict__ tiles, int* __restrict__ n_tiles) {
     extern __shared__ int cnt[];                        // [E] counts, then [E] running places
@@ -117,8 +137,10 @@ __global__ void moe_plan_kernel(const int* __restrict__ sel_e, int n, int E, int
     pdl_wait();
     for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&cnt[sel_e[i]], 1);
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        if ((unsigned)sel_e[i] < (unsigned)E) atomicAdd(&cnt[sel_e[i]], 1);
     __syncthreads();
+    __shared__ int placed;
     if (threadIdx.x == 0) {
         int o = 0, nt = 0;
         for (int e = 0; e < E; ++e) {
@@ -133,9 +155,12 @@ __global__ void moe_plan_kernel(const int* __restrict__ sel_e, int n, int E, int
         }
         offsets[E] = o;
         *n_tiles = nt;
+        placed = o;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += blockDim.x) perm[atomicAdd(&at[sel_e[i]], 1)] = i;
+    for (int i = threadIdx.x; i < n; i += blockDim.x)
+        if ((unsigned)sel_e[i] < (unsigned)E) perm[atomicAdd(&at[sel_e[i]], 1)] = i;
+    for (int i = placed + threadIdx.x; i < n; i += blockDim.x) perm[i] = 0;
 }
 
 // ---- tiles ---------------------------------------------------------------------------------------------
@@ -412,14 +437,26 @@ inline bool mma_takes(int dtype, int K, const void* a, const void* b) {
     return dtype == QNN_DT_BF16 && K % 32 == 0 && ((((uintptr_t)a | (uintptr_t)b) & 15) == 0);
 }
 
+// out[t] = sum over the row's entries of the expert's output, or, for an entry whose expert id is E or more (an
+// identity expert), of its score times the row x[t] itself; plus the shared expert's output, times
+// sigmoid(shared_gate[t]) when the shared expert has a gate.
 __global__ void moe_combine_kernel(const float* __restrict__ ys, int top, const void* __restrict__ shared, int shared_dt,
+                                   const float* __restrict__ shared_gate, const int* __restrict__ sel_e,
+                                   const float* __restrict__ sel_w, int E, const void* __restrict__ x, int x_dt,
                                    float* __restrict__ out, int W, size_t n) {
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const size_t t = i / W, c = i - t * W;
-    float s = shared ? load_as_f(shared, shared_dt, i) : 0.f;
-    for (int k = 0; k < top; ++k) s += ys[(t * top + k) * W + c];
+    float s = 0.f;
+    for (int k = 0; k < top; ++k) {
+        if (sel_e != nullptr && sel_e[t * top + k] >= E) s += sel_w[t * top + k] * load_as_f(x, x_dt, i);
+        else s += ys[(t * top + k) * W + c];
+    }
+    if (shared) {
+        const float v = load_as_f(shared, shared_dt, i);
+        s += shared_gate != nullptr ? v * (1.f / (1.f + expf(-shared_gate[t]))) : v;
+    }
     out[i] = s;
 }
 
@@ -436,16 +473,17 @@ __global__ void gated_act_clamped_kernel(const T* __restrict__ gu, T* __restrict
 }  // namespace
 
 QNN_API int qnn_moe_route(const void* x, int x_dt, const void* w_router, int w_dt, int T, int W, int E, int top,
-                          int score_fn, int renorm, int* sel_e, float* sel_w, cudaStream_t st) {
+                          int score_fn, int renorm, const float* correction, float out_scale, int* sel_e, float* sel_w,
+                          cudaStream_t st) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || top > MAX_TOP || W <= 0) return QNN_ERR_ARGUMENT;
     const int warps = E >= 8 ? 8 : (E >= 4 ? 4 : 2);
-    const size_t smem = (size_t)E * sizeof(float);
+    const size_t smem = (size_t)2 * E * sizeof(float);
     if (smem > 48 * 1024) return QNN_ERR_UNSUPPORTED;
     const dim3 grid(T), block(warps * 32);
 #define QNN_ROUTE(TX, TW)                                                                                         \
     launch_pdl(moe_route_kernel<TX, TW>, grid, block, smem, st, (const TX*)x, (const TW*)w_router, T, W, E, top,  \
-               score_fn, renorm, sel_e, sel_w)
+               score_fn, renorm, correction, out_scale, sel_e, sel_w)
     if (x_dt == QNN_DT_BF16 && w_dt == QNN_DT_BF16) QNN_ROUTE(bf16, bf16);
     else if (x_dt == QNN_DT_BF16) QNN_ROUTE(bf16, float);
     else if (w_dt == QNN_DT_BF16) QNN_ROUTE(float, bf16);
@@ -544,12 +582,15 @@ QNN_API int qnn_moe_down(const void* hidden, int dtype, int ff, const void* w_do
     QNN_LAUNCH_CHECK();
 }
 
-QNN_API int qnn_moe_combine(const float* ys, int top, const void* shared, int shared_dt, float* out, int T, int W,
+// sel_e, sel_w, E, x: given when some expert ids may be E or more (identity experts); null / 0 otherwise.
+QNN_API int qnn_moe_combine(const float* ys, int top, const void* shared, int shared_dt, const float* shared_gate,
+                            const int* sel_e, const float* sel_w, int E, const void* x, int x_dt, float* out, int T, int W,
                             cudaStream_t st) {
     if (T <= 0) return 0;
+    if (sel_e != nullptr && (sel_w == nullptr || x == nullptr)) return QNN_ERR_ARGUMENT;
     const size_t n = (size_t)T * W;
-    launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, ys, top, shared, shared_dt, out, W,
-               n);
+    launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, ys, top, shared, shared_dt,
+               shared_gate, sel_e, sel_w, E, x, x_dt, out, W, n);
     QNN_LAUNCH_CHECK();
 }
 

@@ -7,7 +7,8 @@
 //   * a tile's rows start at the tile list's row, its weights at row e * N of the stacked matrices (TMA coordinates);
 //   * rows of a tile beyond its expert's last row belong to the next expert: they are multiplied and never stored;
 //   * the gated epilogue is the clamped one, g' = min(g, limit), u' = clamp(u, -limit, limit),
-//     g' * sigmoid(alpha g') * (u' + 1), stored as bfloat16 in the gathered order;
+//     g' * sigmoid(alpha g') * (u' + 1), or, with limit <= 0, the plain silu(g) * u; stored as bfloat16 in the
+//     gathered order;
 //   * the plain epilogue stores float32 rows back where the rows came from (the permutation), times the row's score
 //     when the score goes on the output.
 // Every wait on an mbarrier is bounded, as there: when it runs out the thread sets `status` and the CTA still frees
@@ -193,9 +194,14 @@ moe_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     tmem_ld32(lane_addr + BN / 2 + c0, u);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const float g = fminf(__uint_as_float(v[j]), limit);
-                        const float up = fminf(fmaxf(__uint_as_float(u[j]), -limit), limit);
-                        f[j] = __fdividef(g, 1.f + __expf(-alpha * g)) * (up + 1.f);
+                        if (limit > 0.f) {
+                            const float g = fminf(__uint_as_float(v[j]), limit);
+                            const float up = fminf(fmaxf(__uint_as_float(u[j]), -limit), limit);
+                            f[j] = __fdividef(g, 1.f + __expf(-alpha * g)) * (up + 1.f);
+                        } else {                                 // no limit: the plain gate silu(g) * u
+                            const float g = __uint_as_float(v[j]);
+                            f[j] = __fdividef(g, 1.f + __expf(-g)) * __uint_as_float(u[j]);
+                        }
                     }
                 } else {
 #pragma unroll

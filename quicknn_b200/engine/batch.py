@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import dataclasses
-from typing import Any, Mapping, Optional
+from typing import Any, Dict, Mapping, Optional
 
 import torch
 
@@ -68,3 +68,7 @@ class StepBatch:
     whole: Optional[WholeSequences] = None    # extend steps: the sequences with their cached tokens in front
     longest: int = 0                          # decode: class of the longest sequence (an upper bound), 0 = unknown
     spread: float = 0.0                       # decode: class of longest / mean length (1.0, 1.25, 1.6 or 2.2), 0 = unknown
+    # What the writer of a cache line leaves, under the line's index, for the layers that read the line later in the
+    # same step: its packed rows with this step's keys and values as the cache gets them (and their head shape).  A
+    # prompt longer than a ring has lost its first keys from the cache by then; its own rows still have them.
+    shared_rows: Dict[int, Any] = dataclasses.field(default_factory=dict)

@@ -49,6 +49,11 @@ class Model:
             blk.load(local, self.dtype, self.device)
             self.blocks.append(blk)
         self.embedding = tensors[spec.embedding.tensor].contiguous()
+        self.positions = None              # learned position vectors, added to the embedded rows
+        if spec.embedding.position_tensor is not None:
+            self.positions = tensors[spec.embedding.position_tensor].contiguous()
+            if self.positions.shape[0] < spec.max_positions:
+                raise ValueError(f"the position table has {self.positions.shape[0]} rows for {spec.max_positions} positions")
         self.embedding_norm = None
         if spec.embedding.norm is not None:
             self.embedding_norm = NORMS.get(spec.embedding.norm.kind)(spec.embedding.norm)
@@ -60,6 +65,7 @@ class Model:
         if why:
             raise ValueError(f"output head: {why}")
         self._check_schedule()
+        self._lines_read = {e.cache for e in spec.schedule if not e.writes_cache}
 
     # ---- construction --------------------------------------------------------------
     @classmethod
@@ -119,6 +125,8 @@ class Model:
 
     def weight_bytes(self) -> int:
         n = self.embedding.numel() * self.embedding.element_size()
+        if self.positions is not None:
+            n += self.positions.numel() * self.positions.element_size()
         if self.head is not self.embedding:
             n += self.head.numel() * self.head.element_size()
         if self.embedding_norm is not None:
@@ -140,7 +148,14 @@ class Model:
         spec = self.spec
         sched = spec.schedule
         first = self.blocks[sched[0].layer].first_norm() if sched else None
-        if self.embedding_norm is not None:
+        if self.positions is not None and self.embedding_norm is None:
+            # a learned vector per position joins the looked-up row; the first layer's norm in the same kernel
+            if hasattr(first, "of_embedding_rows"):
+                x, normed = first.of_embedding_rows(step.tokens, self.embedding, spec.embedding.scale, self.positions,
+                                                    step.tok_pos, step.act_dtype)
+            else:
+                x, normed = ops.embed_pos(step.tokens, self.embedding, spec.embedding.scale, self.positions, step.tok_pos)
+        elif self.embedding_norm is not None:
             # the normed rows are the stream itself (float32), not a sublayer's input
             x = self.embedding_norm(ops.embed(step.tokens, self.embedding, spec.embedding.scale), torch.float32)
             normed = None
@@ -151,11 +166,14 @@ class Model:
             x, normed = ops.embed(step.tokens, self.embedding, spec.embedding.scale), None
         for i, e in enumerate(sched):
             line = cache.line(e.cache, writes=e.writes_cache)
+            if line is not None:
+                line.has_readers = e.cache in self._lines_read
             # the first norm of the layer that runs next is applied by this one, in the kernel
             # that adds this layer's last sublayer to the residual stream
             nxt = self.blocks[sched[i + 1].layer].first_norm() if i + 1 < len(sched) else None
             out = self.blocks[e.layer].forward(x, step, line, normed=normed, next_norm=nxt)
             x, normed = out if nxt is not None else (out, None)
+        step.shared_rows.clear()               # what layers handed each other lives no longer than the step
         return self.logits_of_rows(x, None if step.want_every_row else step.want_rows, step.act_dtype, reduce)
 
     def logits_of_rows(self, x: torch.Tensor, rows: Optional[torch.Tensor], act_dtype: torch.dtype, reduce=None):

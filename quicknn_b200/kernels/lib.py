@@ -43,20 +43,20 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_gemm_skinny_tcgen05": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_int, c_vp, c_vp],
     "qnn_gemm_skinny_tcgen05_argmax": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_float, c_vp, c_vp, c_vp],
     "qnn_attn_decode": [c_vp, c_ll, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp, c_int, c_int,
-                        c_int, c_int, c_float, c_float, c_int, c_vp, c_vp, c_int, c_vp, c_ll, c_vp],
+                        c_int, c_int, c_float, c_float, c_int, c_vp, c_vp, c_int, c_vp, c_ll, c_vp, c_vp],
     "qnn_attn_extend": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_ll, c_vp, c_vp,
-                        c_vp, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_vp],
+                        c_vp, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_vp, c_vp],
     "qnn_attn_supports": [c_int, c_int, c_int, c_int],
     "qnn_attn_prefill_generic": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_vp, c_vp, c_int, c_int, c_int,
-                                 c_int, c_float, c_float, c_int, c_vp],
+                                 c_int, c_float, c_float, c_int, c_vp, c_vp],
     "qnn_attn_prefill_mma": [c_vp, c_vp, c_vp, c_ll, c_vp, c_ll, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int,
-                             c_float, c_float, c_int, c_vp],
+                             c_float, c_float, c_int, c_vp, c_vp],
     "qnn_attn_prefill_tcgen05": [c_vp, c_ll, c_vp, c_ll, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_float,
-                                 c_float, c_int, c_vp, c_vp],
+                                 c_float, c_int, c_vp, c_vp, c_vp],
     "qnn_attn_extend_gather": [c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int,
                                c_int, c_int, c_int, c_int, c_int, c_vp],
     "qnn_attn_prefill_paged": [c_vp, c_ll, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_ll, c_vp, c_vp,
-                               c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_vp],
+                               c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_vp, c_vp],
     "qnn_sample": [c_vp, c_int, c_int, c_int, c_float, c_float, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
                    c_vp, c_vp],
     "qnn_sample_candidates": [c_vp, c_int, c_int, c_int, c_int, c_float, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
@@ -74,7 +74,7 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_gla_scan_segments": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_float, c_vp, c_vp, c_vp, c_vp,
                               c_vp, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp],
     "qnn_gla_norm_gate": [c_vp, c_ll, c_vp, c_int, c_float, c_vp, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp],
-    "qnn_moe_route": [c_vp, c_int, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp],
+    "qnn_moe_route": [c_vp, c_int, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_float, c_vp, c_vp, c_vp],
     "qnn_moe_tile_rows": [c_int, c_int, c_int, c_int, c_int],
     "qnn_moe_max_tiles": [c_int, c_int, c_int],
     "qnn_moe_plan": [c_vp, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp],
@@ -84,7 +84,7 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_moe_gather": [c_vp, c_int, c_vp, c_vp, c_int, c_int, c_vp, c_int, c_vp],
     "qnn_moe_tcgen05": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int,
                         c_float, c_float, c_vp, c_vp],
-    "qnn_moe_combine": [c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_vp],
+    "qnn_moe_combine": [c_vp, c_int, c_vp, c_int, c_vp, c_vp, c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_vp],
     "qnn_gated_act_clamped": [c_vp, c_vp, c_int, c_int, c_int, c_float, c_float, c_vp],
     "qnn_layernorm": [c_vp, c_int, c_vp, c_int, c_float, c_vp, c_int, c_int, c_int, c_vp],
     "qnn_add_layernorm": [c_vp, c_vp, c_int, c_vp, c_int, c_vp, c_int, c_float, c_vp, c_int, c_int, c_int, c_vp],
@@ -95,10 +95,16 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_activation": [c_vp, c_int, c_vp, c_int, c_ll, c_vp],
     "qnn_head_prep": [c_vp, c_int, c_ll, c_vp, c_int, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                       c_vp, c_int, c_vp, c_vp, c_int, c_float, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_int, c_int,
-                      c_vp, c_int, c_vp],
+                      c_vp, c_int, c_int, c_vp],
     "qnn_memory_scan": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_vp, c_ll, c_float, c_int, c_vp, c_vp, c_vp, c_vp,
                         c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp],
     "qnn_mlstm_gates": [c_vp, c_ll, c_vp, c_int, c_float, c_vp, c_vp, c_vp, c_vp, c_ll, c_vp, c_int, c_int, c_vp],
+    "qnn_group_rmsnorm": [c_vp, c_int, c_vp, c_int, c_float, c_int, c_vp, c_int, c_int, c_int, c_vp],
+    "qnn_add2_group_rmsnorm": [c_vp, c_vp, c_int, c_vp, c_int, c_vp, c_int, c_float, c_int, c_vp, c_int, c_int, c_int, c_vp],
+    "qnn_embed_pos": [c_vp, c_vp, c_int, c_float, c_vp, c_int, c_vp, c_int, c_vp, c_vp, c_int, c_float, c_int, c_vp, c_int,
+                      c_int, c_int, c_int, c_vp],
+    "qnn_sigmoid_gate": [c_vp, c_int, c_ll, c_vp, c_int, c_ll, c_int, c_int, c_vp],
+    "qnn_xielu": [c_vp, c_int, c_float, c_float, c_vp, c_ll, c_vp],
     "qnn_head_norm_gate": [c_vp, c_ll, c_int, c_vp, c_ll, c_vp, c_int, c_int, c_float, c_vp, c_ll, c_int, c_vp, c_ll,
                            c_int, c_int, c_int, c_int, c_vp],
 }

@@ -571,15 +571,24 @@ def linear_refusal(dtype: torch.dtype, inner: int) -> Optional[str]:
     return None
 
 
+def _check_slopes(slopes: Optional[torch.Tensor], n_heads: int) -> None:
+    if slopes is not None:
+        _req(slopes, "slopes", torch.float32, 1)
+        if slopes.numel() != n_heads:
+            raise ValueError(f"attention: {slopes.numel()} distance slopes for {n_heads} query heads")
+
+
 def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_pos: torch.Tensor,
                  tok_row0: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int],
                  seq_row0: Optional[torch.Tensor] = None, seq_len: Optional[torch.Tensor] = None,
-                 max_len: int = 0):
+                 max_len: int = 0, slopes: Optional[torch.Tensor] = None):
     """Causal (optionally windowed) attention of this step's own rows.  qkv: [T, (nq+2nkv)*hd]
     after rotation; returns [T, nq*hd].  bfloat16 with head sizes 64/128/256 runs on the tensor
     cores when the per-sequence arrays (first row, length) are given; everything else takes the
-    generic kernel."""
+    generic kernel.  ``slopes`` (float32, one per query head, optional): ``slope * (i - j)`` is taken off the
+    score of query position i and key position j."""
     _req(qkv, "qkv", None, 2)
+    _check_slopes(slopes, n_heads)
     T = qkv.shape[0]
     out = torch.empty((T, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     es = qkv.element_size()
@@ -595,31 +604,32 @@ def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_
             code = L.qnn_attn_prefill_tcgen05(
                 _p(qkv), T, _p(out), out.shape[1], _p(seq_row0), _p(seq_len), None, seq_row0.numel(), int(max_len),
                 n_heads, n_kv, head_dim, float(scale), float(cap or 0.0), int(window or 0),
-                _p(_status_word(qkv.device)), _stream())
+                _p(_status_word(qkv.device)), _p(slopes), _stream())
             if code != _lib.ERR_UNSUPPORTED:
                 _lib.check(code, "attn_prefill_tcgen05")
                 return out
         code = L.qnn_attn_prefill_mma(
             ctypes.c_void_p(q_ptr), ctypes.c_void_p(k_ptr), ctypes.c_void_p(v_ptr), qkv.shape[1], _p(out),
             out.shape[1], _p(seq_row0), _p(seq_len), seq_row0.numel(), int(max_len), n_heads, n_kv, head_dim,
-            float(scale), float(cap or 0.0), int(window or 0), _stream())
+            float(scale), float(cap or 0.0), int(window or 0), _p(slopes), _stream())
         if code != _lib.ERR_UNSUPPORTED:
             _lib.check(code, "attn_prefill_mma")
             return out
     _lib.check(L.qnn_attn_prefill_generic(
         ctypes.c_void_p(q_ptr), ctypes.c_void_p(k_ptr), ctypes.c_void_p(v_ptr), qkv.shape[1], dt_code(qkv),
         _p(out), out.shape[1], _p(tok_pos), _p(tok_row0), T, n_heads, n_kv, head_dim, float(scale),
-        float(cap or 0.0), int(window or 0), _stream()), "attn_prefill")
+        float(cap or 0.0), int(window or 0), _p(slopes), _stream()), "attn_prefill")
     return out
 
 
 def attn_prefill_paged(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor,
                        v_pool: torch.Tensor, page_table: torch.Tensor, page_size: int, ring: int,
                        tok_pos: torch.Tensor, tok_slot: torch.Tensor, scale: float, cap: Optional[float],
-                       window: Optional[int]):
+                       window: Optional[int], slopes: Optional[torch.Tensor] = None):
     """Several query rows per sequence against the paged cache (keys written earlier in the
     same step by the layer that owns the line).  q = the first nq*hd columns of qkv."""
     _req(qkv, "qkv", None, 2)
+    _check_slopes(slopes, n_heads)
     _req(k_pool, "k_pool", qkv.dtype, 4)
     _req(v_pool, "v_pool", qkv.dtype, 4)
     T = qkv.shape[0]
@@ -628,14 +638,15 @@ def attn_prefill_paged(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int
     _lib.check(L.qnn_attn_prefill_paged(
         _p(qkv), qkv.shape[1], dt_code(qkv), _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1],
         page_size, ring, _p(out), out.shape[1], _p(tok_pos), _p(tok_slot), T, n_heads, n_kv, head_dim,
-        float(scale), float(cap or 0.0), int(window or 0), _stream()), "attn_prefill_paged")
+        float(scale), float(cap or 0.0), int(window or 0), _p(slopes), _stream()), "attn_prefill_paged")
     return out
 
 
 def attn_shared_tensor_core(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor,
                             v_pool: torch.Tensor, page_table: torch.Tensor, page_size: int, ring: int, slots: torch.Tensor,
                             seq_row0: torch.Tensor, seq_len: torch.Tensor, scale: float, cap: Optional[float],
-                            window: Optional[int], longest: int, whole=None) -> Optional[torch.Tensor]:
+                            window: Optional[int], longest: int, whole=None,
+                            slopes: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """Attention of query rows ``q`` ([rows, n_heads * head_dim]) whose keys and values, this step's positions included,
     are in the paged cache already (a layer that reads the line another layer wrote earlier in the step), on the
     tensor-core prompt kernel: keys and values are copied out of the pages beside the queries into whole sequences,
@@ -644,6 +655,7 @@ def attn_shared_tensor_core(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: 
     if not (ATTN_TCGEN05 and q.dtype == torch.bfloat16 and head_dim in (64, 128, 256)):
         return None
     _req(q, "q", torch.bfloat16, 2)
+    _check_slopes(slopes, n_heads)
     L = _lib.load()
     width = (n_heads + 2 * n_kv) * head_dim
     if whole is None:
@@ -659,7 +671,7 @@ def attn_shared_tensor_core(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: 
     out_rows = torch.empty((total, n_heads * head_dim), dtype=q.dtype, device=q.device)
     code = L.qnn_attn_prefill_tcgen05(
         _p(rows), total, _p(out_rows), out_rows.shape[1], _p(row0), _p(length), _p(start), B, most, n_heads, n_kv,
-        head_dim, float(scale), float(cap or 0.0), int(window or 0), _p(_status_word(q.device)), _stream())
+        head_dim, float(scale), float(cap or 0.0), int(window or 0), _p(_status_word(q.device)), _p(slopes), _stream())
     if code == _lib.ERR_UNSUPPORTED:
         return None
     _lib.check(code, "attn_prefill_tcgen05")
@@ -668,7 +680,8 @@ def attn_shared_tensor_core(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: 
 
 def attn_extend(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
                 page_table: torch.Tensor, page_size: int, ring: int, tok_pos: torch.Tensor, tok_row0: torch.Tensor,
-                tok_slot: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int], whole=None):
+                tok_slot: torch.Tensor, scale: float, cap: Optional[float], window: Optional[int], whole=None,
+                slopes: Optional[torch.Tensor] = None):
     """Attention of a step that continues sequences by several tokens: each row sees the cached
     positions before its sequence's first row of this step (from the cache, as earlier steps left it)
     and this step's own rows from there to itself (from ``qkv``, already rotated).  The caller appends
@@ -680,6 +693,7 @@ def attn_extend(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_poo
     the query tiles that lie before each sequence's new rows, and the new rows' outputs are picked out.
     The generic kernel walks the keys once per row and kv head: it serves float32 and the other head sizes."""
     _req(qkv, "qkv", None, 2)
+    _check_slopes(slopes, n_heads)
     _req(k_pool, "k_pool", qkv.dtype, 4)
     _req(v_pool, "v_pool", qkv.dtype, 4)
     for n, t in (("tok_pos", tok_pos), ("tok_row0", tok_row0), ("tok_slot", tok_slot)):
@@ -698,7 +712,7 @@ def attn_extend(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_poo
         code = L.qnn_attn_prefill_tcgen05(
             _p(rows), whole.total, _p(out_rows), out_rows.shape[1], _p(whole.row0), _p(whole.length), _p(whole.start), B,
             whole.longest, n_heads, n_kv, head_dim, float(scale), float(cap or 0.0), int(window or 0),
-            _p(_status_word(qkv.device)), _stream())
+            _p(_status_word(qkv.device)), _p(slopes), _stream())
         if code != _lib.ERR_UNSUPPORTED:
             _lib.check(code, "attn_prefill_tcgen05")
             return gather_rows(out_rows, whole.tok_row, qkv.dtype)
@@ -712,19 +726,21 @@ def attn_extend(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_poo
         ctypes.c_void_p(q_ptr), ctypes.c_void_p(k_ptr), ctypes.c_void_p(v_ptr), qkv.shape[1], dt_code(qkv),
         _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1], page_size, ring, _p(out), out.shape[1],
         _p(tok_pos), _p(tok_row0), _p(tok_slot), T, n_heads, n_kv, head_dim, float(scale), float(cap or 0.0),
-        int(window or 0), _stream()), "attn_extend")
+        int(window or 0), _p(slopes), _stream()), "attn_extend")
     return out
 
 
 def attn_decode(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_pool: torch.Tensor,
                 v_pool: torch.Tensor, page_table: torch.Tensor, page_size: int, ring: int,
                 slots: torch.Tensor, slot_len: torch.Tensor, scale: float, cap: Optional[float],
-                window: Optional[int], n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor):
+                window: Optional[int], n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor,
+                slopes: Optional[torch.Tensor] = None):
     """One query row per sequence against the paged cache.  q = the first nq*hd columns of qkv.
     ``slots``, ``slot_len`` and ``page_table`` must be complete before the kernel that runs just before
     this one on the stream starts (host copies and earlier kernels are): the tensor-core kernel reads
     them while that kernel may still run."""
     _req(qkv, "qkv", None, 2)
+    _check_slopes(slopes, n_heads)
     B = qkv.shape[0]
     _req(k_pool, "k_pool", qkv.dtype, 4)
     _req(v_pool, "v_pool", qkv.dtype, 4)
@@ -739,7 +755,7 @@ def attn_decode(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, k_poo
     _lib.check(L.qnn_attn_decode(
         _p(qkv), qkv.shape[1], dt_code(qkv), _p(k_pool), _p(v_pool), _p(page_table), page_table.shape[1],
         page_size, ring, _p(slots), _p(slot_len), B, n_heads, n_kv, head_dim, float(scale), float(cap or 0.0),
-        int(window or 0), _p(part_o), _p(part_ml), n_splits, _p(out), out.shape[1], _stream()), "attn_decode", 2)
+        int(window or 0), _p(part_o), _p(part_ml), n_splits, _p(out), out.shape[1], _p(slopes), _stream()), "attn_decode", 2)
     return out
 
 
@@ -894,6 +910,18 @@ def copy_cols(src: torch.Tensor, dst: torch.Tensor, dst_col0: int) -> torch.Tens
     return dst
 
 
+def copy_col_range(src: torch.Tensor, src_col0: int, n: int, dst: torch.Tensor, dst_col0: int) -> torch.Tensor:
+    """dst[:, dst_col0 : dst_col0 + n] = src[:, src_col0 : src_col0 + n], rows of the same element type."""
+    _req(src, "src", None, 2)
+    _req(dst, "dst", src.dtype, 2)
+    T = src.shape[0]
+    if dst.shape[0] != T or src_col0 + n > src.shape[1] or dst_col0 + n > dst.shape[1]:
+        raise ValueError("copy_col_range: shapes do not agree")
+    _lib.check(_lib.load().qnn_copy_rows(_col_ptr(src, src_col0), dt_code(src), src.shape[1], _col_ptr(dst, dst_col0),
+                                         dst.shape[1], T, n, _stream()), "copy_rows")
+    return dst
+
+
 def scale_heads(x: torch.Tensor, gate_logits: torch.Tensor, n_heads: int) -> torch.Tensor:
     """x[t, h, :] *= sigmoid(gate_logits[t, h]) in place; the gate is float32."""
     _req(x, "x", None, 2)
@@ -1012,20 +1040,27 @@ MOE_SCORES = {"sigmoid": 0, "softmax": 1}
 GATED_CLAMPED = 2            # the gated activation g' * sigmoid(alpha g') * (u' + 1) of clamped g', u'
 
 
-def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False):
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False,
+              correction: Optional[torch.Tensor] = None, scale: float = 1.0):
     """(expert ids int32 [rows*top], scores float32 [rows*top]): the ``top`` best experts of every row by
-    score(x w_router^T), logits and scores in float32, ties to the lower index."""
+    score(x w_router^T), logits and scores in float32, ties to the lower index.  With ``correction`` (float32, one per
+    expert) the experts are ranked by score + correction and weighted by the score alone.  ``scale`` multiplies the
+    weights (after the renormalisation, if any)."""
     _req(x, "x", None, 2)
     _req(w_router, "w_router", None, 2)
     T, W = x.shape
     E = w_router.shape[0]
     if w_router.shape[1] != W:
         raise ValueError("moe_route: the router's inner size differs from the rows'")
+    if correction is not None:
+        _req(correction, "correction", torch.float32, 1)
+        if correction.numel() != E:
+            raise ValueError("moe_route: a correction per expert")
     sel_e = torch.empty(T * top, dtype=torch.int32, device=x.device)
     sel_w = torch.empty(T * top, dtype=torch.float32, device=x.device)
     _lib.check(_lib.load().qnn_moe_route(_p(x), dt_code(x), _p(w_router), dt_code(w_router), T, W, E, int(top),
-                                         MOE_SCORES[score], int(renormalize), _p(sel_e), _p(sel_w), _stream()),
-               "moe_route")
+                                         MOE_SCORES[score], int(renormalize), _p(correction), float(scale), _p(sel_e),
+                                         _p(sel_w), _stream()), "moe_route")
     return sel_e, sel_w
 
 
@@ -1034,8 +1069,13 @@ MOE_GROUPED_FROM = 64        # rows per expert (on average) from which prompts t
 
 def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: int, w_gate_up: torch.Tensor,
                 w_down: torch.Tensor, activation: int, limit: float, alpha: float, weight_on_input: bool,
-                shared: Optional[torch.Tensor] = None, grouped: Optional[bool] = None) -> torch.Tensor:
+                shared: Optional[torch.Tensor] = None, grouped: Optional[bool] = None,
+                shared_gate: Optional[torch.Tensor] = None, identity: bool = False) -> torch.Tensor:
     """sum over a row's chosen experts of down_e(act(gate_e(x'), up_e(x'))) (+ ``shared``), float32 [rows, width].
+    ``activation``: ``GATED_CLAMPED`` or the code of a plain gate (act(g) * u, e.g. ``ACT_CODES["silu"]``).
+    ``identity``: expert ids from the number of experts on are identity experts (their output is the row itself
+    times the score); they take no part in the products.  ``shared_gate`` (float32 [rows]): the shared expert's
+    output is multiplied by its sigmoid.
     The score multiplies the expert's input (x' = score * x) or its output.  w_gate_up: [experts, 2*ff, width]
     (gate rows, then up rows); w_down: [experts, width, ff].  Everything stays on the device.
 
@@ -1055,8 +1095,11 @@ def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: 
     n = T * top
     if grouped is None:
         grouped = n >= MOE_GROUPED_FROM * E
-    grouped = bool(grouped and USE_TCGEN05 and x.dtype == torch.bfloat16 and activation == GATED_CLAMPED
-                   and W % 8 == 0 and ff % 8 == 0)
+    grouped = bool(grouped and USE_TCGEN05 and x.dtype == torch.bfloat16
+                   and activation in (GATED_CLAMPED, ACT_CODES["silu"]) and W % 8 == 0 and ff % 8 == 0)
+    if activation != GATED_CLAMPED:
+        limit = 0.0                                 # the grouped product's epilogue reads "no limit" as silu(g) * u
+    extra = (shared_gate, (sel_e, sel_w, E, x) if identity else None)
     tile_rows = 128 if grouped else int(L.qnn_moe_tile_rows(n, E, dt_code(x), W, ff))   # else 16, or 64 with many rows each
     max_tiles = int(L.qnn_moe_max_tiles(n, E, tile_rows))
     meta = torch.empty(E + 1 + n + 2 * max_tiles + 1, dtype=torch.int32, device=x.device)
@@ -1076,30 +1119,38 @@ def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: 
                                  _stream())
         if code == _lib.ERR_UNSUPPORTED:           # sizes the grouped product refuses: the other tiles
             return moe_experts(x, sel_e, sel_w, top, w_gate_up, w_down, activation, limit, alpha, weight_on_input, shared,
-                               grouped=False)
+                               grouped=False, shared_gate=shared_gate, identity=identity)
         _lib.check(code, "moe_tcgen05")
         _lib.check(L.qnn_moe_tcgen05(_p(hidden), _p(w_down), _p(ys), n, E, W, ff, EPI_NONE, _p(offsets), _p(perm), _p(sel_w),
                                      _p(tiles), _p(n_tiles), max_tiles, int(not weight_on_input), 0.0, 0.0, status,
                                      _stream()), "moe_tcgen05")
-        return _moe_sum(L, ys, top, shared, T, W)
+        return _moe_sum(L, ys, top, shared, T, W, *extra)
     _lib.check(L.qnn_moe_gate_up(_p(x), dt_code(x), W, _p(w_gate_up), ff, _p(offsets), _p(perm), _p(sel_w), _p(tiles),
                                  _p(n_tiles), max_tiles, tile_rows, top, int(weight_on_input), int(activation), float(limit),
                                  float(alpha), _p(hidden), _stream()), "moe_gate_up")
     _lib.check(L.qnn_moe_down(_p(hidden), dt_code(x), ff, _p(w_down), W, _p(offsets), _p(perm), _p(sel_w), _p(tiles),
                               _p(n_tiles), max_tiles, tile_rows, int(not weight_on_input), _p(ys), _stream()), "moe_down")
-    return _moe_sum(L, ys, top, shared, T, W)
+    return _moe_sum(L, ys, top, shared, T, W, *extra)
 
 
-def _moe_sum(L, ys: torch.Tensor, top: int, shared: Optional[torch.Tensor], T: int, W: int) -> torch.Tensor:
-    """out[t] = sum over the row's experts (+ the shared expert's output), float32."""
-    if top == 1 and shared is None:
+def _moe_sum(L, ys: torch.Tensor, top: int, shared: Optional[torch.Tensor], T: int, W: int,
+             shared_gate: Optional[torch.Tensor] = None, identity=None) -> torch.Tensor:
+    """out[t] = sum over the row's experts (+ the shared expert's output, gated or not), float32.  ``identity``:
+    (expert ids, scores, number of experts, rows) when ids from that number on stand for the row itself."""
+    if top == 1 and shared is None and identity is None:
         return ys
+    if shared_gate is not None:
+        _req(shared_gate, "shared_gate", torch.float32)
+        if shared is None or shared_gate.numel() != T:
+            raise ValueError("moe_experts: a gate per row, for a shared expert")
+    sel_e, sel_w, E, x = identity if identity is not None else (None, None, 0, None)
     if shared is not None:
         _req(shared, "shared", None, 2)
         if tuple(shared.shape) != (T, W):
             raise ValueError("moe_experts: the shared expert's output has another shape")
     out = torch.empty((T, W), dtype=torch.float32, device=ys.device)
-    _lib.check(L.qnn_moe_combine(_p(ys), top, _p(shared), dt_code(shared) if shared is not None else 0, _p(out), T, W,
+    _lib.check(L.qnn_moe_combine(_p(ys), top, _p(shared), dt_code(shared) if shared is not None else 0, _p(shared_gate),
+                                 _p(sel_e), _p(sel_w), int(E), _p(x), dt_code(x) if x is not None else 0, _p(out), T, W,
                                  _stream()), "moe_combine")
     return out
 
@@ -1225,14 +1276,17 @@ def head_prep(src: torch.Tensor, col0: int, n_q: int, n_k: int, n_v_cols: int, h
               q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None, norm_dim: int = 0,
               eps: float = 0.0, rot_dim: int = 0, inv_freq: Optional[torch.Tensor] = None, interleaved: bool = False,
               tok_pos: Optional[torch.Tensor] = None, tok_slot: Optional[torch.Tensor] = None, line=None,
-              append: bool = False) -> torch.Tensor:
+              append: bool = False, norm_whole: bool = False) -> torch.Tensor:
     """Bias, an RMS norm per head of queries and keys, rotation and the append to a cache line, in one kernel.
 
     ``src``: rows that hold, from column ``col0`` on, ``n_q`` query heads and ``n_k`` key heads of ``head_dim`` columns
     and then ``n_v_cols`` value columns.  ``dst`` (default: in place) gets the same layout from ``dst_col0`` on in its
     own element type.  ``bias``: over those columns.  ``q_norm`` / ``k_norm``: weights [norm_dim] of a norm over the
     first ``norm_dim`` columns of each head.  ``rot_dim``: rotated columns per head, by ``tok_pos * inv_freq``, pairs
-    (j, j + rot_dim/2) or, ``interleaved``, (2j, 2j + 1).  ``append``: keys and values go to ``line``."""
+    (j, j + rot_dim/2) or, ``interleaved``, (2j, 2j + 1).  ``append``: keys and values go to ``line``.
+    ``norm_whole``: one norm over all query heads together and one over all key heads together instead of one per
+    head (the first ``norm_dim`` columns of every head count); the weights are then [n_q * norm_dim] and
+    [n_k * norm_dim]."""
     _req(src, "src", None, 2)
     T = src.shape[0]
     width = (n_q + n_k) * head_dim + n_v_cols
@@ -1248,12 +1302,14 @@ def head_prep(src: torch.Tensor, col0: int, n_q: int, n_k: int, n_v_cols: int, h
         if bias.numel() != width:
             raise ValueError(f"head_prep: the bias has {bias.numel()} elements for {width} columns")
     wdt = 0
-    for w in (q_norm, k_norm):
+    for w, heads in ((q_norm, n_q), (k_norm, n_k)):
         if w is not None:
             _req(w, "norm weight", None, 1)
-            if w.numel() != norm_dim:
+            if w.numel() != (norm_dim * heads if norm_whole else norm_dim):
                 raise ValueError("head_prep: a norm weight per normed column")
             wdt = dt_code(w)
+    if norm_whole and ((n_q > 0 and q_norm is None) or (n_k > 0 and k_norm is None)):
+        raise ValueError("head_prep: a norm over all heads needs weights for the queries and for the keys")
     if q_norm is not None and k_norm is not None and q_norm.dtype != k_norm.dtype:
         raise TypeError("head_prep: the two norm weights have one element type")
     if rot_dim:
@@ -1276,7 +1332,7 @@ def head_prep(src: torch.Tensor, col0: int, n_q: int, n_k: int, n_v_cols: int, h
         _col_ptr(src, col0), dt_code(src), src.shape[1], _col_ptr(dst, dst_col0), dt_code(dst), dst.shape[1], T, n_q, n_k,
         n_v_cols, head_dim, int(norm_dim), int(rot_dim), int(interleaved), _p(bias), dt_code(bias) if bias is not None else 0,
         _p(q_norm), _p(k_norm), wdt, float(eps), _p(inv_freq) if rot_dim else None, _p(tok_pos), _p(tok_slot), _p(k_pool),
-        _p(v_pool), _p(table), max_pages, page_size, ring, _p(slot_len), int(append), _stream()), "head_prep")
+        _p(v_pool), _p(table), max_pages, page_size, ring, _p(slot_len), int(append), int(norm_whole), _stream()), "head_prep")
     return dst
 
 
@@ -1395,3 +1451,90 @@ def head_norm_gate(o: torch.Tensor, head_stride: int, n_heads: int, vdim: int, e
         _col_ptr(gate, g_col), gate.shape[1], {"silu": 0, "sigmoid": 1}[gate_act], _p(out), out.shape[1], dt_code(gate), T,
         n_heads, vdim, _stream()), "head_norm_gate")
     return out
+
+
+# ---- norms in groups, sublayers side by side, learned positions, gates per element -----------------------------------------
+
+def group_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, groups: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """RMS norm in ``groups`` equal consecutive pieces of every row, each divided by its own
+    sqrt(mean(piece^2) + eps), the whole times ``weight``; float32 sums."""
+    _req(x, "x", None, 2)
+    _req(weight, "weight", None, 1)
+    T, H = x.shape
+    if weight.numel() != H or groups < 1 or H % groups:
+        raise ValueError(f"group_rmsnorm: {weight.numel()} weights, {groups} groups for width {H}")
+    out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+    _lib.check(_lib.load().qnn_group_rmsnorm(_p(x), dt_code(x), _p(weight), dt_code(weight), float(eps), int(groups), _p(out),
+                                             dt_code(out), T, H, _stream()), "group_rmsnorm")
+    return out
+
+
+def add2_group_rmsnorm(resid: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor] = None,
+                       w_next: Optional[torch.Tensor] = None, eps: float = 0.0, groups: int = 1,
+                       out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """resid += a + b (float32 stream, in place; either may be None); returns the grouped norm of the new stream
+    with ``w_next`` when that is given, in one kernel."""
+    _req(resid, "resid", torch.float32, 2)
+    T, H = resid.shape
+    for name, t in (("a", a), ("b", b)):
+        if t is not None:
+            _req(t, name, None, 2)
+            if tuple(t.shape) != (T, H):
+                raise ValueError("add2_group_rmsnorm: shapes do not agree")
+    out = None
+    if w_next is not None:
+        _req(w_next, "w_next", None, 1)
+        if w_next.numel() != H or groups < 1 or H % groups:
+            raise ValueError(f"add2_group_rmsnorm: {w_next.numel()} weights, {groups} groups for width {H}")
+        out = torch.empty((T, H), dtype=out_dtype, device=resid.device)
+    _lib.check(_lib.load().qnn_add2_group_rmsnorm(
+        _p(resid), _p(a), dt_code(a) if a is not None else 0, _p(b), dt_code(b) if b is not None else 0, _p(w_next),
+        dt_code(w_next) if w_next is not None else 0, float(eps), int(groups), _p(out),
+        dt_code(out) if out is not None else 0, T, H, _stream()), "add2_group_rmsnorm")
+    return out
+
+
+def embed_pos(tokens: torch.Tensor, table: torch.Tensor, scale: float, pos_table: torch.Tensor, tok_pos: torch.Tensor,
+              w_norm: Optional[torch.Tensor] = None, eps: float = 0.0, groups: int = 1,
+              out_dtype: Optional[torch.dtype] = None):
+    """table[token] * scale + pos_table[position] as float32 rows; with ``w_norm`` also their grouped norm, in the
+    same kernel: (rows, normed rows or None)."""
+    _req(tokens, "tokens", torch.int32, 1)
+    _req(tok_pos, "tok_pos", torch.int32, 1)
+    _req(table, "table", None, 2)
+    _req(pos_table, "pos_table", None, 2)
+    T, (V, H) = tokens.numel(), table.shape
+    if pos_table.shape[1] != H or tok_pos.numel() < T:
+        raise ValueError("embed_pos: the position table has another width, or positions are missing")
+    out = torch.empty((T, H), dtype=torch.float32, device=tokens.device)
+    normed = None
+    if w_norm is not None:
+        _req(w_norm, "w_norm", None, 1)
+        if w_norm.numel() != H or groups < 1 or H % groups:
+            raise ValueError(f"embed_pos: {w_norm.numel()} weights, {groups} groups for width {H}")
+        normed = torch.empty((T, H), dtype=out_dtype, device=tokens.device)
+    _lib.check(_lib.load().qnn_embed_pos(
+        _p(tokens), _p(table), dt_code(table), float(scale), _p(pos_table), dt_code(pos_table), _p(tok_pos),
+        pos_table.shape[0], _p(out), _p(w_norm), dt_code(w_norm) if w_norm is not None else 0, float(eps), int(groups),
+        _p(normed), dt_code(normed) if normed is not None else 0, T, H, V, _stream()), "embed_pos")
+    return out, normed
+
+
+def sigmoid_gate_(o: torch.Tensor, g: torch.Tensor, g_col0: int = 0) -> torch.Tensor:
+    """o[t, c] *= sigmoid(g[t, g_col0 + c]) in place: a gate per element, its logits in columns of rows that may be
+    wider (a piece of a stacked product)."""
+    _req(o, "o", None, 2)
+    _req(g, "g", None, 2)
+    T, N = o.shape
+    if g.shape[0] != T or g_col0 + N > g.shape[1]:
+        raise ValueError("sigmoid_gate_: shapes do not agree")
+    _lib.check(_lib.load().qnn_sigmoid_gate(_p(o), dt_code(o), N, _col_ptr(g, g_col0), dt_code(g), g.shape[1], T, N,
+                                            _stream()), "sigmoid_gate")
+    return o
+
+
+def xielu_(x: torch.Tensor, ap: float, an: float) -> torch.Tensor:
+    """In place: x > 0: ap x^2 + x / 2; x <= 0: an (exp(x) - 1 - x) + x / 2."""
+    _req(x, "x")
+    _lib.check(_lib.load().qnn_xielu(_p(x), dt_code(x), float(ap), float(an), _p(x), x.numel(), _stream()), "xielu")
+    return x

@@ -17,6 +17,12 @@ Options beyond that (all off unless the spec gives them):
 * ``bias``: biases on the q, k, v and o products (``q_bias`` ... ``o_bias``).
 * ``qk_norm`` = {"eps": e}: an RMS norm over ``head_dim`` per query head and key head with the weights ``q_norm`` /
   ``k_norm`` (shared by the heads), before the rotation.
+  With ``"over": "projection"`` it is one norm over the whole query projection (all heads together) and one over the
+  whole key projection, with weights of those sizes.
+* ``distance_slopes``: one number per query head; ``slope * (i - j)`` is taken off the score of query position i and
+  key position j (a bias that grows with the distance, in float32 inside the attention kernels).
+* ``out_gate``: the concatenated heads are multiplied, element by element, by sigmoid(``g_proj`` x) before the output
+  product.
 * ``shared_kv``: the layer has no keys and values of its own; its schedule entry reads the cache line that another
   layer writes (whose head counts, sizes and rotation are the same), with its own queries.
 
@@ -60,6 +66,13 @@ class AttentionMixer(Mixer):
         self.has_bias = bool(p.get("bias", False))
         self.qk_norm = p.get("qk_norm")
         self.shared_kv = bool(p.get("shared_kv", False))
+        self.norm_whole = bool(self.qk_norm) and self.qk_norm.get("over", "head") == "projection"
+        self.out_gate = bool(p.get("out_gate", False))
+        self._slope_values = None if p.get("distance_slopes") is None else tuple(float(v) for v in p["distance_slopes"])
+        if self._slope_values is not None and len(self._slope_values) != self.n_heads:
+            raise ValueError(f"{len(self._slope_values)} distance slopes for {self.n_heads} heads")
+        self.slopes: Optional[torch.Tensor] = None
+        self.w_out_gate: Optional[torch.Tensor] = None
         if p.get("v_head_dim") and (self.value_dim != self.key_dim or self.key_dim % 8):
             self.head_dim = (max(self.key_dim, self.value_dim) + 7) // 8 * 8
         self.heads = HeadShape(self.n_heads, 0 if self.shared_kv else self.n_kv, self.head_dim)
@@ -91,9 +104,12 @@ class AttentionMixer(Mixer):
             if not shared:
                 out.update({"k_bias": ((nkv * hd,), B), "v_bias": ((nkv * vd,), B)})
         if p.get("qk_norm"):
-            out["q_norm"] = ((hd,), S)
+            whole = p["qk_norm"].get("over", "head") == "projection"
+            out["q_norm"] = ((nq * hd if whole else hd,), S)
             if not shared:
-                out["k_norm"] = ((hd,), S)
+                out["k_norm"] = ((nkv * hd if whole else hd,), S)
+        if p.get("out_gate", False):
+            out["g_proj"] = ((nq * vd, H), M)
         return out
 
     def _carried(self, t: torch.Tensor, heads: int, size: int) -> torch.Tensor:
@@ -120,12 +136,17 @@ class AttentionMixer(Mixer):
             w_o = wide.reshape(w_o.shape[0], self.n_heads * D)
         self.w_o = w_o.contiguous()
         self.out_bias = tensors["o_bias"].contiguous() if self.has_bias else None
+        if self.out_gate:                                    # zero rows where the carried values are zero
+            self.w_out_gate = self._carried(tensors["g_proj"], self.n_heads, vd).contiguous()
+        if self._slope_values is not None:
+            self.slopes = torch.tensor(self._slope_values, dtype=torch.float32, device=device)
         if self.has_bias or self.qk_norm:
             self.prep = HeadPrep(
                 bias=torch.cat([b.to(torch.float32) for b in biases]).contiguous() if biases else None,
                 q_norm=tensors["q_norm"].contiguous() if self.qk_norm else None,
                 k_norm=tensors["k_norm"].contiguous() if self.qk_norm and not self.shared_kv else None,
-                norm_dim=kd if self.qk_norm else 0, eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0)
+                norm_dim=kd if self.qk_norm else 0, eps=float(self.qk_norm["eps"]) if self.qk_norm else 0.0,
+                whole=self.norm_whole)
         self.position.prepare(device)
         # sizes that the kernels do not take are refused here, when the model is built, not at its first step
         why = (ops.attention_refusal(compute_dtype, self.n_heads, self.n_kv, self.head_dim)
@@ -140,7 +161,7 @@ class AttentionMixer(Mixer):
         self._resident = sms * max(1, min(8, 512 // max(1, self.head_dim)))
 
     def weight_bytes(self) -> int:
-        ws = [self.w_qkv, self.w_o, self.out_bias]
+        ws = [self.w_qkv, self.w_o, self.out_bias, self.w_out_gate]
         if self.prep is not None:
             ws += [self.prep.bias, self.prep.q_norm, self.prep.k_norm]
         return sum(w.numel() * w.element_size() for w in ws if w is not None)
@@ -208,8 +229,26 @@ class AttentionMixer(Mixer):
                 self.position.place(qkv, h, step, line, append=not extend)
             else:
                 self.position.place(qkv, h, step, line, append=not extend, prep=self.prep)
-        y = project(self.attend(qkv, step, line), self.w_o)
+        if line.has_readers and line.writes and not self.shared_kv and step.mode == "prefill":
+            step.shared_rows[line.index] = (qkv, h)          # for the layers that read this line later in the step
+        a = self.attend(qkv, step, line)
+        if self.out_gate:
+            a = ops.sigmoid_gate_(a, project(x, self.w_out_gate))
+        y = project(a, self.w_o)
         return y if (self.out_bias is None or self.defer_out_bias) else ops.add_bias_(y, self.out_bias)
+
+    def _attend_rows_of(self, left, q: torch.Tensor, step) -> torch.Tensor:
+        """Attention of the query rows ``q`` over the keys and values in the packed rows ``left`` = (rows, head shape)
+        that the writer of the cache line left for this step (whole prompts)."""
+        rows, shape = left
+        D, nkv = self.head_dim, self.n_kv
+        if shape.head_dim != D or shape.n_kv_heads != nkv or rows.shape[0] != q.shape[0] or rows.dtype != q.dtype:
+            raise ValueError("the rows that the cache line's writer left do not fit this layer's heads")
+        packed = torch.empty((q.shape[0], (self.n_heads + 2 * nkv) * D), dtype=q.dtype, device=q.device)
+        ops.copy_col_range(q, 0, self.n_heads * D, packed, 0)
+        ops.copy_col_range(rows, shape.n_heads * D, 2 * nkv * D, packed, self.n_heads * D)
+        return ops.attn_prefill(packed, self.n_heads, nkv, D, step.tok_pos, step.tok_row0, self.scale, self.softcap,
+                                self.window, step.seq_row0, step.seq_len, step.max_q_len, slopes=self.slopes)
 
     def attend(self, qkv: torch.Tensor, step, line) -> torch.Tensor:
         """Attention of the packed q|k|v rows of a step, by the step's mode.  In prefill and decode the keys and
@@ -222,12 +261,18 @@ class AttentionMixer(Mixer):
             # so that the first rows still find the ring cells that the last rows overwrite
             a = ops.attn_extend(qkv, h.n_heads, h.n_kv_heads, h.head_dim, line.k, line.v, line.page_table,
                                 line.page_size, line.ring, step.tok_pos, step.tok_row0, step.tok_slot, self.scale,
-                                self.softcap, self.window, whole=getattr(step, "whole", None))
+                                self.softcap, self.window, whole=getattr(step, "whole", None), slopes=self.slopes)
             ops.cache_append(qkv, h.n_heads, h.n_kv_heads, h.head_dim, step.tok_pos, step.tok_slot, line)
         elif step.mode != "decode" and (not line.writes or self.shared_kv):
             # the keys of this line were written by another layer earlier in this step; in a ring the last
             # rows of the step have by then overwritten cells: whole prompts may fill the ring, a step that
             # continues a sequence may bring only as many rows as the ring has cells beyond the window
+            left = step.shared_rows.get(line.index) if step.mode == "prefill" else None
+            if left is not None and qkv.shape[1] == self.n_heads * self.head_dim:
+                # whole prompts: this step's keys and values are the rows that the line's writer left, so the layer
+                # attends over packed rows of its own queries beside them, like the writer itself (a prompt longer than
+                # a ring is no matter then)
+                return self._attend_rows_of(left, qkv, step)
             room = line.ring - ((self.window or line.ring) - 1 if extend else 0)
             if line.ring and step.max_q_len > room:
                 raise ValueError(f"a step of {step.max_q_len} tokens overruns the ring of {line.ring} "
@@ -239,19 +284,21 @@ class AttentionMixer(Mixer):
                 a = ops.attn_shared_tensor_core(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v,
                                                 line.page_table, line.page_size, line.ring, step.slots, step.seq_row0,
                                                 step.seq_len, self.scale, self.softcap, self.window, step.max_q_len,
-                                                whole=whole)
+                                                whole=whole, slopes=self.slopes)
             if a is None:
                 a = ops.attn_prefill_paged(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v,
                                            line.page_table, line.page_size, line.ring, step.tok_pos, step.tok_slot,
-                                           self.scale, self.softcap, self.window)
+                                           self.scale, self.softcap, self.window, slopes=self.slopes)
         elif step.mode == "prefill":
             a = ops.attn_prefill(qkv, self.n_heads, self.n_kv, self.head_dim, step.tok_pos, step.tok_row0,
-                                 self.scale, self.softcap, self.window, step.seq_row0, step.seq_len, step.max_q_len)
+                                 self.scale, self.softcap, self.window, step.seq_row0, step.seq_len, step.max_q_len,
+                                 slopes=self.slopes)
         else:
             splits = self.decode_splits(step)
             n = step.n_seqs * self.n_heads * splits
             part = step.scratch.view(torch.float32)
             a = ops.attn_decode(qkv, self.n_heads, self.n_kv, self.head_dim, line.k, line.v, line.page_table,
                                 line.page_size, line.ring, step.slots, line.slot_len, self.scale, self.softcap,
-                                self.window, splits, part[:n * self.head_dim], part[n * self.head_dim:n * (self.head_dim + 2)])
+                                self.window, splits, part[:n * self.head_dim], part[n * self.head_dim:n * (self.head_dim + 2)],
+                                slopes=self.slopes)
         return a

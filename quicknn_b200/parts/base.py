@@ -111,13 +111,15 @@ class HeadShape:
 class HeadPrep:
     """What a mixer wants done to the packed q|k|v rows before their positions are placed: a bias over the packed row
     (None: none) and an RMS norm over the first ``norm_dim`` columns of every query and key head with the weights
-    ``q_norm`` / ``k_norm`` (None: no norm).  Tensors on the device."""
+    ``q_norm`` / ``k_norm`` (None: no norm); with ``whole`` one norm over all query heads together and one over all
+    key heads together, the weights then one per head and column.  Tensors on the device."""
 
     bias: Any = None
     q_norm: Any = None
     k_norm: Any = None
     norm_dim: int = 0
     eps: float = 0.0
+    whole: bool = False
 
 
 class Part:

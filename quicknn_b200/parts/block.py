@@ -10,6 +10,10 @@ feed-forward that a layer may lack.
 is normed (a layer norm here; any norm unfused).  A mixer's ``out_bias`` and the mean of a ``parallel`` mixer's
 branches are formed inside the kernel that norms and adds.
 
+``parallel``: h = norm(x);  x += mixer(h) + ff(h): one norm, both sublayers read its output, and their sum is
+added to the stream (a layer may lack the feed-forward).  With a ``group_rmsnorm`` the add and the next layer's
+norm are one kernel.
+
 The residual stream is float32 in both precisions.  When the norms are RMSNorm the
 post-norm, the add and the next pre-norm run as one kernel; that also holds across the
 border of two layers: ``forward`` may be handed its input already normed (``normed``) and
@@ -23,7 +27,7 @@ import torch
 
 from ..kernels import ops
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block
-from .norm import LayerNorm, NoNorm, RMSNorm
+from .norm import GroupRMSNorm, LayerNorm, NoNorm, RMSNorm
 from .parallel import ParallelMixer
 from .spec import LayerSpec, PartSpec
 
@@ -201,3 +205,29 @@ class PostNormBlock(_LayerParts):
         if next_norm is None:
             return resid
         return resid, (n if handed else next_norm(resid, act))
+
+
+@BLOCKS.register("parallel")
+class ParallelBlock(_LayerParts):
+    """h = norm(x); x += mixer(h) + ff(h)."""
+
+    NORM_NAMES = ("pre",)
+
+    @classmethod
+    def norm_names(cls, layer: LayerSpec) -> Tuple[str, ...]:
+        return cls.NORM_NAMES
+
+    def first_norm(self):
+        return self.norms["pre"]
+
+    def forward(self, resid: torch.Tensor, step, line, normed=None, next_norm=None):
+        act = step.act_dtype
+        h = normed if normed is not None else self.norms["pre"](resid, act)
+        a = self.mixer.forward(h, step, line)
+        f = self.ff.forward(h, step) if self.ff is not None else None
+        if isinstance(next_norm, GroupRMSNorm):
+            return resid, next_norm.after_add(resid, a, f, act)
+        ops.add2_group_rmsnorm(resid, a, f)
+        if next_norm is not None:
+            return resid, next_norm(resid, act)
+        return resid

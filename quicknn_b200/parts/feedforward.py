@@ -1,4 +1,6 @@
 """Feed-forward parts.  ``gated_mlp``: down(act(gate(x)) * up(x)).  ``mlp``: down(act(up(x))), without a gate.
+``mlp`` also takes the activation ``xielu`` with two learned numbers p, q per layer (the parameter ``act_params``):
+z > 0: softplus(p) z^2 + z / 2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2.
 
 Reference: two products and a GO_GEGLU dispatch, then the down product
 (src/models/QuickNN.Models.Gemma2.pas:184-187; gelu_tanh at shaders/tensor.comp:23).
@@ -8,6 +10,8 @@ activation is the product's epilogue.
 from __future__ import annotations
 
 from typing import Dict, Optional, Tuple
+
+import math
 
 import torch
 
@@ -52,15 +56,16 @@ class GatedMLP(FeedForward):
 
 @FEED_FORWARDS.register("mlp")
 class MLP(FeedForward):
-    """down(act(up(x))) with ``activation`` one of ``ops.ACT_CODES`` (``relu2``: the square of relu)."""
+    """down(act(up(x))) with ``activation`` one of ``ops.ACT_CODES`` (``relu2``: the square of relu) or ``xielu``."""
 
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
         self.activation = str(spec.params["activation"])
-        if self.activation not in ops.ACT_CODES:
-            raise ValueError(f"activation {self.activation!r} is not one of {sorted(ops.ACT_CODES)}")
+        if self.activation != "xielu" and self.activation not in ops.ACT_CODES:
+            raise ValueError(f"activation {self.activation!r} is not one of {sorted(ops.ACT_CODES) + ['xielu']}")
+        self.xielu = (0.0, 0.0)           # softplus(p), 1/2 + softplus(q)
         self.w_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
@@ -68,14 +73,25 @@ class MLP(FeedForward):
     def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         H, I = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
         M = cls.PARAM_ROLE_MATRIX
-        return {"up_proj": ((I, H), M), "down_proj": ((H, I), M)}
+        out = {"up_proj": ((I, H), M), "down_proj": ((H, I), M)}
+        if str(spec.params["activation"]) == "xielu":
+            out["act_params"] = ((2,), cls.PARAM_ROLE_NORM)
+        return out
 
     def load(self, tensors, compute_dtype, device) -> None:
         self.w_up = tensors["up_proj"].contiguous()
         self.w_down = tensors["down_proj"].contiguous()
+        if self.activation == "xielu":
+            # the two constants once, when the model is built (float64 on the host, rounded to float32 by the kernel's
+            # arguments)
+            p, q = (float(v) for v in tensors["act_params"].detach().to("cpu", torch.float64).tolist())
+            softplus = lambda z: max(z, 0.0) + math.log1p(math.exp(-abs(z)))          # noqa: E731
+            self.xielu = (softplus(p), 0.5 + softplus(q))
 
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.w_up, self.w_down))
 
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
+        if self.activation == "xielu":
+            return project(ops.xielu_(project(x, self.w_up), *self.xielu), self.w_down)
         return project(project(x, self.w_up, epilogue=ops.EPI_ACT, activation=self.activation), self.w_down)

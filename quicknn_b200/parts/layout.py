@@ -17,6 +17,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
         out[name] = (tuple(shape), role)
 
     put(spec.embedding.tensor, (spec.embedding.vocab_size, spec.embedding.hidden_size), Part.PARAM_ROLE_MATRIX)
+    if spec.embedding.position_tensor is not None:
+        put(spec.embedding.position_tensor, (spec.embedding.n_positions, spec.embedding.hidden_size), Part.PARAM_ROLE_MATRIX)
     if spec.embedding.norm is not None:
         for k, (shape, role) in NORMS.get(spec.embedding.norm.kind).param_shapes(spec.embedding.norm).items():
             put(spec.embedding.norm_tensor if k == "weight" else f"{spec.embedding.norm_tensor}.{k}", shape, role)

@@ -7,7 +7,12 @@ act = g * sigmoid(alpha * g) * (u + 1)  (alpha 1.702 unless given).
 scores.  Router logits and scores are float32; scores are sigmoid(logit) (or a softmax over the experts), optionally
 renormalised over the chosen ones; the score multiplies the expert's *input* (``weight_on`` = "input": the
 sum over the chosen experts of expert(score * x)) or its output.  A shared expert of the same form, with sizes and
-limit of its own, may run for every token beside them.  Everything from the router to the sum stays on the
+limit of its own, may run for every token beside them.  Options: ``activation`` "silu" (the plain gate
+silu(gate) * up instead of the clamped one; no ``limit``); ``correction`` (a learned number per expert that is
+added to the scores for the choice only; the weights are the scores without it); ``route_scale`` (multiplies the
+weights); ``identity`` = n (the router has n more outputs than there are experts; those stand for identity
+experts, whose output is the input itself times the weight, and which have no tensors); ``shared_gate`` (the shared
+expert's output is multiplied by sigmoid(w . x), one number per token).  Everything from the router to the sum stays on the
 device (no count is read back), so a decode step with routed layers is captured in a CUDA graph like any other.
 """
 from __future__ import annotations
@@ -60,17 +65,29 @@ class RoutedExperts(FeedForward):
         self.n_experts = int(p["experts"])
         self.top = int(p["top"])
         self.inter = int(p["intermediate_size"])
-        self.limit = float(p["limit"])
+        self.activation = str(p.get("activation", "clamped"))
+        if self.activation not in ("clamped", "silu"):
+            raise ValueError(f"routed experts: activation {self.activation!r} is neither 'clamped' nor 'silu'")
+        self.limit = float(p["limit"]) if self.activation == "clamped" else 0.0
         self.alpha = float(p.get("alpha", 1.702))
+        self.identity = int(p.get("identity", 0))
+        self.has_correction = bool(p.get("correction", False))
+        self.route_scale = float(p.get("route_scale", 1.0))
+        self.has_shared_gate = bool(p.get("shared_gate", False))
         self.score = str(p.get("score", "sigmoid"))
         self.renormalize = bool(p.get("renormalize", False))
         self.weight_on_input = str(p.get("weight_on", "input")) == "input"
-        if not (1 <= self.top <= self.n_experts) or self.top > 16:
-            raise ValueError(f"routed experts: top {self.top} of {self.n_experts} experts (at most 16)")
+        if self.identity < 0 or not (1 <= self.top <= self.n_experts + self.identity) or self.top > 16:
+            raise ValueError(f"routed experts: top {self.top} of {self.n_experts} experts and {self.identity} identity "
+                             f"experts (at most 16)")
         if self.score not in ops.MOE_SCORES:
             raise ValueError(f"routed experts: score {self.score!r} is not one of {sorted(ops.MOE_SCORES)}")
         shared: Optional[PartSpec] = p.get("shared")
         self.shared = None if shared is None else FEED_FORWARDS.get(shared.kind)(shared)
+        if self.has_shared_gate and self.shared is None:
+            raise ValueError("routed experts: a gate for a shared expert that is not there")
+        self.correction: Optional[torch.Tensor] = None
+        self.w_shared_gate: Optional[torch.Tensor] = None
         self.w_router: Optional[torch.Tensor] = None
         self.w_gate_up: Optional[torch.Tensor] = None      # [experts, 2 * ff, width]
         self.w_down: Optional[torch.Tensor] = None         # [experts, width, ff]
@@ -80,7 +97,11 @@ class RoutedExperts(FeedForward):
         p = spec.params
         H, I, E = int(p["hidden_size"]), int(p["intermediate_size"]), int(p["experts"])
         M = cls.PARAM_ROLE_MATRIX
-        out: Dict[str, Tuple[Tuple[int, ...], str]] = {"router": ((E, H), M)}
+        out: Dict[str, Tuple[Tuple[int, ...], str]] = {"router": ((E + int(p.get("identity", 0)), H), M)}
+        if p.get("correction", False):
+            out["correction"] = ((E + int(p.get("identity", 0)),), cls.PARAM_ROLE_NORM)
+        if p.get("shared_gate", False):
+            out["shared_gate"] = ((1, H), M)
         for e in range(E):
             out[f"experts.{e}.gate_proj"] = ((I, H), M)
             out[f"experts.{e}.up_proj"] = ((I, H), M)
@@ -100,17 +121,25 @@ class RoutedExperts(FeedForward):
         if self.w_gate_up.dtype != self.w_down.dtype:
             wide = torch.float32
             self.w_gate_up, self.w_down = self.w_gate_up.to(wide), self.w_down.to(wide)
+        if self.has_correction:
+            self.correction = tensors["correction"].to(torch.float32).contiguous()
+        if self.has_shared_gate:
+            self.w_shared_gate = tensors["shared_gate"].contiguous()
         if self.shared is not None:
             self.shared.load({k[len("shared."):]: v for k, v in tensors.items() if k.startswith("shared.")},
                              compute_dtype, device)
 
     def weight_bytes(self) -> int:
-        n = sum(w.numel() * w.element_size() for w in (self.w_router, self.w_gate_up, self.w_down))
+        n = sum(w.numel() * w.element_size() for w in (self.w_router, self.w_gate_up, self.w_down, self.correction,
+                                                       self.w_shared_gate) if w is not None)
         return n + (self.shared.weight_bytes() if self.shared is not None else 0)
 
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
-        sel_e, sel_w = ops.moe_route(x, self.w_router, self.top, self.score, self.renormalize)
+        sel_e, sel_w = ops.moe_route(x, self.w_router, self.top, self.score, self.renormalize, self.correction,
+                                     self.route_scale)
         shared = self.shared.forward(x, step) if self.shared is not None else None
+        gate = ops.small_linear_f32(x, self.w_shared_gate) if self.has_shared_gate else None
         xe = x if x.dtype == self.w_gate_up.dtype else ops.cast(x, self.w_gate_up.dtype)
-        return ops.moe_experts(xe, sel_e, sel_w, self.top, self.w_gate_up, self.w_down, ops.GATED_CLAMPED, self.limit,
-                               self.alpha, self.weight_on_input, shared)
+        act = ops.GATED_CLAMPED if self.activation == "clamped" else ops.ACT_CODES["silu"]
+        return ops.moe_experts(xe, sel_e, sel_w, self.top, self.w_gate_up, self.w_down, act, self.limit,
+                               self.alpha, self.weight_on_input, shared, shared_gate=gate, identity=self.identity > 0)

@@ -5,6 +5,8 @@
 (src/backends/vulkan/shaders/tensor.comp:63-72; Operations.pas:129-149); the
 reference's files hold 1 + w already (src/models/QuickNN.Models.Gemma2.pas:58), the
 checkpoints read here hold w.
+``group_rmsnorm``: the row is cut into ``groups`` equal consecutive pieces, each is divided by its own
+sqrt(mean(piece^2) + eps), and the whole is multiplied by w (one group: an RMS norm with a plain weight).
 """
 from __future__ import annotations
 
@@ -51,6 +53,39 @@ class RMSNorm(Norm):
             return ops.add_rmsnorm(resid, y, self.weight, self.eps, self.unit_offset)
         return ops.add_rmsnorm(resid, y, self.weight, self.eps, self.unit_offset,
                                then.weight, then.eps, then.unit_offset, out_dtype)
+
+
+@NORMS.register("group_rmsnorm")
+class GroupRMSNorm(Norm):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.groups = int(spec.get("groups", 1))
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"group_rmsnorm: {self.groups} groups do not divide the width {self.size}")
+        self.weight: Optional[torch.Tensor] = None
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        return {"weight": ((int(spec.params["size"]),), cls.PARAM_ROLE_SCALE)}
+
+    def load(self, tensors, compute_dtype, device) -> None:
+        self.weight = tensors["weight"].contiguous()
+
+    def weight_bytes(self) -> int:
+        return self.weight.numel() * self.weight.element_size()
+
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        return ops.group_rmsnorm(x, self.weight, self.eps, self.groups, out_dtype)
+
+    def of_embedding_rows(self, tokens, table, scale: float, pos_table, tok_pos, out_dtype: torch.dtype):
+        """(embedded rows with their position vectors, self(those rows)) in one kernel."""
+        return ops.embed_pos(tokens, table, scale, pos_table, tok_pos, self.weight, self.eps, self.groups, out_dtype)
+
+    def after_add(self, resid: torch.Tensor, a, b, out_dtype: torch.dtype) -> torch.Tensor:
+        """resid += a + b, then self(resid), in one kernel."""
+        return ops.add2_group_rmsnorm(resid, a, b, self.weight, self.eps, self.groups, out_dtype)
 
 
 @NORMS.register("layernorm")

@@ -43,7 +43,8 @@ def _prepare_and_place(prep, qkv, heads: HeadShape, step, line, append, rot_dim,
                   k_norm=prep.k_norm if prep else None, norm_dim=prep.norm_dim if prep else 0,
                   eps=prep.eps if prep else 0.0, rot_dim=rot_dim, inv_freq=inv_freq, interleaved=interleaved,
                   tok_pos=step.tok_pos, tok_slot=step.tok_slot, line=line,
-                  append=bool(append and line is not None and line.writes and heads.n_kv_heads > 0))
+                  append=bool(append and line is not None and line.writes and heads.n_kv_heads > 0),
+                  norm_whole=bool(prep.whole) if prep else False)
 
 
 @POSITIONS.register("rotary")

@@ -55,6 +55,8 @@ class EmbeddingSpec:
     tensor: str                       # checkpoint name of the table
     norm: Optional[PartSpec] = None   # a norm that the looked-up rows pass through before they become the stream
     norm_tensor: str = ""
+    position_tensor: Optional[str] = None   # checkpoint name of a table [positions, hidden_size] of learned position
+    n_positions: int = 0                    # vectors, added to the looked-up rows (not scaled); its number of rows
 
 
 @dataclasses.dataclass(frozen=True)

@@ -7,6 +7,7 @@ wanted only (the reference: the last row), final norm, the tied head and the sof
 """
 from __future__ import annotations
 
+import dataclasses
 from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
@@ -112,6 +113,13 @@ class Model:
             if e.writes_cache:
                 needs[e.cache] = self.blocks[e.layer].mixer.cache_need()
                 states[e.cache] = self.blocks[e.layer].mixer.state_need()
+        for e in self.spec.schedule:
+            # a line keeps what the widest of its readers sees: a reader's window may be longer than its writer's
+            # (or absent), and then the line's ring has to hold that many positions
+            if not e.writes_cache and needs[e.cache] is not None:
+                mine, kept = self.blocks[e.layer].mixer.cache_need(), needs[e.cache]
+                if mine is not None and kept.window is not None and (mine.window is None or mine.window > kept.window):
+                    needs[e.cache] = dataclasses.replace(kept, window=mine.window)
         return needs, states
 
     def scratch_need(self, step) -> int:

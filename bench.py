@@ -285,6 +285,17 @@ def design_sizes(name, design="fuposun"):
                  query_pre_attn_scalar=hd)
     if design == "fuposun":
         return [("fuposun", fupo), ("gemma2", gemma)]
+    if design == "mubasun":
+        matt = {"heads": heads, "kv_heads": kvh, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window}}
+        mmoe = {"kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4},
+                "router": {"experts": 16, "identity": 2, "top": 2, "scale": 2.5}}
+        mlayers = []
+        for i in range(layers):
+            mixer = matt if i % 4 < 2 else dict(matt, kv_from=i - 2)
+            mlayers.append({"type": "attention", "mixer": mixer, "mlp": mmoe if i % 2 else dense})
+        muba = dict(architecture="Mubasun", vocab=vocab, width=W, max_positions=8192, norm={"eps": 1e-6, "groups": 4},
+                    layers=mlayers)
+        return [("mubasun", muba), ("fuposun", fupo), ("gemma2", gemma)]
     mh = W // (2 * d)                                          # memory heads: the linear-attention layer's sizes
     att = {"heads": heads, "kv_heads": kvh, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "rot": {"base": 1e4, "dims": hd}}
     left = dict(att, mask={"size": window},
@@ -382,7 +393,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-baseline", action="store_true", help="do not time the plain PyTorch / NumPy baselines")
-    ap.add_argument("--design", default=None, choices=["fuposun", "tumudra"],
+    ap.add_argument("--design", default=None, choices=["fuposun", "tumudra", "mubasun"],
                     help="instead of the record: this design beside the library's other models at equal size "
                          "(prefill, decode, kernels)")
     ap.add_argument("--design-sizes", default="1b,2b", help="with --design: which of 1b, 2b")

@@ -137,11 +137,21 @@ __global__ void xielu_kernel(const void* __restrict__ x, int dt, float ap, float
 
 static size_t norm_smem(int H) { return ((size_t)H + NORM_WARPS) * sizeof(float); }
 
+// A row is held in shared memory as float32: rows beyond 48 KB need the kernel's limit raised, rows beyond what an SM
+// has are refused.
+template <typename K>
+static bool row_fits(K kernel, int H) {
+    const size_t need = norm_smem(H);
+    if (need <= 48 * 1024) return true;
+    if (need > 227 * 1024) return false;
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)need) == cudaSuccess;
+}
+
 QNN_API int qnn_group_rmsnorm(const void* x, int x_dt, const void* w, int w_dt, float eps, int groups, void* out,
                               int out_dt, int T, int H, cudaStream_t st) {
     if (T <= 0) return 0;
     if (groups < 1 || H % groups) return QNN_ERR_ARGUMENT;
-    if (norm_smem(H) > 48 * 1024) return QNN_ERR_UNSUPPORTED;
+    if (!row_fits(group_rmsnorm_kernel, H)) return QNN_ERR_UNSUPPORTED;
     launch_pdl(group_rmsnorm_kernel, dim3(T), dim3(NORM_THREADS), norm_smem(H), st, x, x_dt, w, w_dt, eps, groups, out, out_dt,
                H);
     QNN_LAUNCH_CHECK();
@@ -152,7 +162,7 @@ QNN_API int qnn_add2_group_rmsnorm(float* resid, const void* a, int a_dt, const 
                                    float eps, int groups, void* out, int out_dt, int T, int H, cudaStream_t st) {
     if (T <= 0) return 0;
     if (out != nullptr && (groups < 1 || H % groups || w == nullptr)) return QNN_ERR_ARGUMENT;
-    if (norm_smem(H) > 48 * 1024) return QNN_ERR_UNSUPPORTED;
+    if (!row_fits(add2_group_rmsnorm_kernel, H)) return QNN_ERR_UNSUPPORTED;
     launch_pdl(add2_group_rmsnorm_kernel, dim3(T), dim3(NORM_THREADS), norm_smem(H), st, resid, a, a_dt, b, b_dt, w, w_dt, eps,
                groups < 1 ? 1 : groups, out, out_dt, H);
     QNN_LAUNCH_CHECK();
@@ -164,7 +174,7 @@ QNN_API int qnn_embed_pos(const int* tokens, const void* table, int t_dt, float 
                           void* normed, int n_dt, int T, int H, int V, cudaStream_t st) {
     if (T <= 0) return 0;
     if (normed != nullptr && (groups < 1 || H % groups || w == nullptr)) return QNN_ERR_ARGUMENT;
-    if (norm_smem(H) > 48 * 1024) return QNN_ERR_UNSUPPORTED;
+    if (!row_fits(embed_pos_kernel, H)) return QNN_ERR_UNSUPPORTED;
     launch_pdl(embed_pos_kernel, dim3(T), dim3(NORM_THREADS), norm_smem(H), st, tokens, table, t_dt, scale, pos_table, p_dt,
                tok_pos, n_pos, out, w, w_dt, eps, groups < 1 ? 1 : groups, normed, n_dt, H, V);
     QNN_LAUNCH_CHECK();

@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 import dataclasses
-from typing import Any, Dict, Mapping, Optional
+from typing import Any, Dict, List, Mapping, Optional
 
 import torch
 
@@ -72,3 +72,7 @@ class StepBatch:
     # same step: its packed rows with this step's keys and values as the cache gets them (and their head shape).  A
     # prompt longer than a ring has lost its first keys from the cache by then; its own rows still have them.
     shared_rows: Dict[int, Any] = dataclasses.field(default_factory=dict)
+    # Calls that a layer leaves for the end of the step, run in order once the last layer is through: a step that
+    # continues sequences appends to a cache line with readers only then, so that the readers still find the ring as
+    # earlier steps left it.
+    after_layers: List[Any] = dataclasses.field(default_factory=list)

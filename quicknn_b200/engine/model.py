@@ -172,6 +172,7 @@ class Model:
             x, normed = first.of_embedding(step.tokens, self.embedding, spec.embedding.scale, step.act_dtype)
         else:
             x, normed = ops.embed(step.tokens, self.embedding, spec.embedding.scale), None
+        step.after_layers.clear()
         for i, e in enumerate(sched):
             line = cache.line(e.cache, writes=e.writes_cache)
             if line is not None:
@@ -181,6 +182,9 @@ class Model:
             nxt = self.blocks[sched[i + 1].layer].first_norm() if i + 1 < len(sched) else None
             out = self.blocks[e.layer].forward(x, step, line, normed=normed, next_norm=nxt)
             x, normed = out if nxt is not None else (out, None)
+        for call in step.after_layers:         # appends that waited for the readers of their cache line
+            call()
+        step.after_layers.clear()
         step.shared_rows.clear()               # what layers handed each other lives no longer than the step
         return self.logits_of_rows(x, None if step.want_every_row else step.want_rows, step.act_dtype, reduce)
 

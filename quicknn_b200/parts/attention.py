@@ -229,7 +229,7 @@ class AttentionMixer(Mixer):
                 self.position.place(qkv, h, step, line, append=not extend)
             else:
                 self.position.place(qkv, h, step, line, append=not extend, prep=self.prep)
-        if line.has_readers and line.writes and not self.shared_kv and step.mode == "prefill":
+        if line.has_readers and line.writes and not self.shared_kv and step.mode != "decode":
             step.shared_rows[line.index] = (qkv, h)          # for the layers that read this line later in the step
         a = self.attend(qkv, step, line)
         if self.out_gate:
@@ -237,9 +237,11 @@ class AttentionMixer(Mixer):
         y = project(a, self.w_o)
         return y if (self.out_bias is None or self.defer_out_bias) else ops.add_bias_(y, self.out_bias)
 
-    def _attend_rows_of(self, left, q: torch.Tensor, step) -> torch.Tensor:
-        """Attention of the query rows ``q`` over the keys and values in the packed rows ``left`` = (rows, head shape)
-        that the writer of the cache line left for this step (whole prompts)."""
+    def _attend_rows_of(self, left, q: torch.Tensor, step, line) -> torch.Tensor:
+        """Attention of the query rows ``q`` (the first columns of its rows) over the keys and values in the packed rows
+        ``left`` = (rows, head shape) that the writer of the cache line left for this step: whole prompts over those
+        rows alone; a step that continues sequences over the cache as earlier steps left it and those rows from there
+        on (the writer appends them when the step's last layer is through)."""
         rows, shape = left
         D, nkv = self.head_dim, self.n_kv
         if shape.head_dim != D or shape.n_kv_heads != nkv or rows.shape[0] != q.shape[0] or rows.dtype != q.dtype:
@@ -247,6 +249,10 @@ class AttentionMixer(Mixer):
         packed = torch.empty((q.shape[0], (self.n_heads + 2 * nkv) * D), dtype=q.dtype, device=q.device)
         ops.copy_col_range(q, 0, self.n_heads * D, packed, 0)
         ops.copy_col_range(rows, shape.n_heads * D, 2 * nkv * D, packed, self.n_heads * D)
+        if step.mode == "extend":
+            return ops.attn_extend(packed, self.n_heads, nkv, D, line.k, line.v, line.page_table, line.page_size,
+                                   line.ring, step.tok_pos, step.tok_row0, step.tok_slot, self.scale, self.softcap,
+                                   self.window, whole=getattr(step, "whole", None), slopes=self.slopes)
         return ops.attn_prefill(packed, self.n_heads, nkv, D, step.tok_pos, step.tok_row0, self.scale, self.softcap,
                                 self.window, step.seq_row0, step.seq_len, step.max_q_len, slopes=self.slopes)
 
@@ -262,17 +268,21 @@ class AttentionMixer(Mixer):
             a = ops.attn_extend(qkv, h.n_heads, h.n_kv_heads, h.head_dim, line.k, line.v, line.page_table,
                                 line.page_size, line.ring, step.tok_pos, step.tok_row0, step.tok_slot, self.scale,
                                 self.softcap, self.window, whole=getattr(step, "whole", None), slopes=self.slopes)
-            ops.cache_append(qkv, h.n_heads, h.n_kv_heads, h.head_dim, step.tok_pos, step.tok_slot, line)
+            append = lambda: ops.cache_append(qkv, h.n_heads, h.n_kv_heads, h.head_dim, step.tok_pos, step.tok_slot, line)  # noqa: E731
+            if line.has_readers and hasattr(step, "after_layers"):
+                step.after_layers.append(append)             # the line's readers come first: see _attend_rows_of
+            else:
+                append()
         elif step.mode != "decode" and (not line.writes or self.shared_kv):
             # the keys of this line were written by another layer earlier in this step; in a ring the last
             # rows of the step have by then overwritten cells: whole prompts may fill the ring, a step that
             # continues a sequence may bring only as many rows as the ring has cells beyond the window
-            left = step.shared_rows.get(line.index) if step.mode == "prefill" else None
-            if left is not None and qkv.shape[1] == self.n_heads * self.head_dim:
-                # whole prompts: this step's keys and values are the rows that the line's writer left, so the layer
-                # attends over packed rows of its own queries beside them, like the writer itself (a prompt longer than
-                # a ring is no matter then)
-                return self._attend_rows_of(left, qkv, step)
+            left = step.shared_rows.get(line.index)
+            if left is not None and (extend or qkv.shape[1] == self.n_heads * self.head_dim):
+                # this step's keys and values are the rows that the line's writer left, so the layer attends over
+                # packed rows of its own queries beside them, like the writer itself (a prompt longer than a ring, or
+                # a portion longer than the ring's spare cells, is no matter then)
+                return self._attend_rows_of(left, qkv, step, line)
             room = line.ring - ((self.window or line.ring) - 1 if extend else 0)
             if line.ring and step.max_q_len > room:
                 raise ValueError(f"a step of {step.max_q_len} tokens overruns the ring of {line.ring} "

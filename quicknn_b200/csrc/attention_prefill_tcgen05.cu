@@ -427,19 +427,22 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 l_sum += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
             } else {
             float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+            // the distance bias of the tile's first column; a column adds slope_u times its place in the tile, so the
+            // bias costs one multiply-add per score and no conversion
+            const float bias0 = slope_u * (float)(col0 - row);
             if (interior) {
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
-                    float x = cap > 0.f ? tanh_fast(s[c] * k1) : s[c] * k1;
-                    x = fmaf(slope_u, (float)(col0 + c - row), x);
+                    const float bias = fmaf(slope_u, (float)c, bias0);     // (float)c is a constant of the unrolled loop
+                    const float x = cap > 0.f ? tanh_fast(s[c] * k1) + bias : fmaf(s[c], k1, bias);
                     s[c] = x;
                     mx4[c & 3] = fmaxf(mx4[c & 3], x);
                 }
             } else {
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
-                    float x = cap > 0.f ? tanh_fast(s[c] * k1) : s[c] * k1;
-                    x = fmaf(slope_u, (float)(col0 + c - row), x);
+                    const float bias = fmaf(slope_u, (float)c, bias0);
+                    float x = cap > 0.f ? tanh_fast(s[c] * k1) + bias : fmaf(s[c], k1, bias);
                     const bool seen = (unsigned)(col0 + c - key_lo) <= key_span;      // key_lo <= column <= key_hi
                     x = seen ? x : -CUDART_INF_F;
                     s[c] = x;

@@ -140,6 +140,7 @@ __device__ __forceinline__ float silu(float x) { return x / (1.f + expf(-x)); }
 #define QNN_ACT_GELU_TANH 0
 #define QNN_ACT_SILU 1
 #define QNN_ACT_RELU2 2          // the square of relu
+#define QNN_ACT_XIELU 3          // xIELU, whose two constants come beside the code (ActConsts)
 // A product without a gate whose epilogue is an activation gets the activation's code plus this as its `act`
 // argument (with the epilogue code "none"): act(x W^T).  Codes below it mean what they meant.
 #define QNN_ACT_ALONE 16
@@ -163,6 +164,12 @@ __device__ __forceinline__ float activate_fast(float x, int act) {
     if (act == QNN_ACT_SILU) return __fdividef(x, 1.f + __expf(-x));
     if (act == QNN_ACT_RELU2) return relu2(x);
     return 0.5f * x * (1.f + tanh_approx(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+// Constants of an activation that has some; xIELU: a = softplus(p), b = 1/2 + softplus(q).
+struct ActConsts { float a, b; };
+__device__ __forceinline__ float activate_fast(float x, int act, ActConsts k) {
+    if (act == QNN_ACT_XIELU) return x > 0.f ? fmaf(k.a * x, x, 0.5f * x) : fmaf(k.b, __expf(x) - 1.f - x, 0.5f * x);
+    return activate_fast(x, act);
 }
 
 }  // namespace qnn

@@ -67,7 +67,7 @@ __device__ __forceinline__ bool has_failed(Barriers* b) { return *reinterpret_ca
 template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    bf16* __restrict__ C, int M, int N, int K, int act, int* __restrict__ status) {
+                    bf16* __restrict__ C, int M, int N, int K, int act, ActConsts actk, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the operand ring wants 1024-byte alignment (8 swizzled rows); the barriers follow it
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -199,7 +199,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
                     if (act >= QNN_ACT_ALONE) {              // an activation without a gate: act(A B^T)
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] = activate_fast(f[j], act - QNN_ACT_ALONE);
+                        for (int j = 0; j < 32; ++j) f[j] = activate_fast(f[j], act - QNN_ACT_ALONE, actk);
                     }
                 }
                 if (c0 + 32 >= OUT_COLS) {
@@ -237,7 +237,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // means a bounded wait ran out (bit 0 producer, bits 1 and 3 tensor-core issue, bit 2 epilogue) and C is
 // not valid.  K must be a multiple of 8 (16-byte row pitch) and the bases 16-byte aligned.
 QNN_API int qnn_gemm_tcgen05(const void* A, const void* B, void* C, int M, int N, int K, int epi, int act,
-                             int* status, cudaStream_t st) {
+                             float act_a, float act_b, int* status, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || ((((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) != 0)) return QNN_ERR_UNSUPPORTED;
     if (epi != EPI_NONE && epi != EPI_GATED) return QNN_ERR_ARGUMENT;
@@ -268,7 +268,7 @@ QNN_API int qnn_gemm_tcgen05(const void* A, const void* B, void* C, int M, int N
             if (e != cudaSuccess) return (int)e;
             configured = true;
         }
-        cudaError_t e = qnn::launch_pdl(kern, grid, dim3(GEMM_THREADS), smem, st, map_a, map_b, (bf16*)C, M, N, K, act, status);
+        cudaError_t e = qnn::launch_pdl(kern, grid, dim3(GEMM_THREADS), smem, st, map_a, map_b, (bf16*)C, M, N, K, act, ActConsts{act_a, act_b}, status);
         return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
     }
     auto kern = gemm_tcgen05_kernel<EPI_NONE>;
@@ -278,6 +278,6 @@ QNN_API int qnn_gemm_tcgen05(const void* A, const void* B, void* C, int M, int N
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cudaError_t e = qnn::launch_pdl(kern, grid, dim3(GEMM_THREADS), smem, st, map_a, map_b, (bf16*)C, M, N, K, act, status);
+    cudaError_t e = qnn::launch_pdl(kern, grid, dim3(GEMM_THREADS), smem, st, map_a, map_b, (bf16*)C, M, N, K, act, ActConsts{act_a, act_b}, status);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

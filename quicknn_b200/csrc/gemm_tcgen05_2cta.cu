@@ -82,7 +82,7 @@ __device__ __forceinline__ bool has_failed(Barriers* b) { return *reinterpret_ca
 template <int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         bf16* __restrict__ C, int M, int N, int K, int act, int* __restrict__ status) {
+                         bf16* __restrict__ C, int M, int N, int K, int act, ActConsts actk, int* __restrict__ status) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* staging = smem + STAGES * STAGE_BYTES;
@@ -225,7 +225,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                             for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
                             if (act >= QNN_ACT_ALONE) {      // an activation without a gate: act(A B^T)
 #pragma unroll
-                                for (int j = 0; j < 32; ++j) f[j] = activate_fast(f[j], act - QNN_ACT_ALONE);
+                                for (int j = 0; j < 32; ++j) f[j] = activate_fast(f[j], act - QNN_ACT_ALONE, actk);
                             }
                         }
                         if (c0 + 32 >= OUT_COLS) {
@@ -273,7 +273,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
                     if (act >= QNN_ACT_ALONE) {              // an activation without a gate: act(A B^T)
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) f[j] = activate_fast(f[j], act - QNN_ACT_ALONE);
+                        for (int j = 0; j < 32; ++j) f[j] = activate_fast(f[j], act - QNN_ACT_ALONE, actk);
                     }
                 }
                 if (c0 + 32 >= OUT_COLS) {
@@ -311,7 +311,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 // Returns QNN_ERR_UNSUPPORTED when the device cannot hold a pair (the caller then uses the single-CTA
 // kernel).
 QNN_API int qnn_gemm_tcgen05_2cta(const void* A, const void* B, void* C, int M, int N, int K, int epi, int act,
-                                  int* status, cudaStream_t st) {
+                                  float act_a, float act_b, int* status, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K & 7) || ((((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) != 0)) return QNN_ERR_UNSUPPORTED;
     if (epi != EPI_NONE && epi != EPI_GATED) return QNN_ERR_ARGUMENT;
@@ -333,7 +333,7 @@ QNN_API int qnn_gemm_tcgen05_2cta(const void* A, const void* B, void* C, int M, 
     const long long ntiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((Nout + cols - 1) / cols);
     if (ntiles > 0x3fffffffLL) return QNN_ERR_UNSUPPORTED;
     const size_t smem = (size_t)STAGES * STAGE_BYTES + STAGING_BYTES + sizeof(Barriers) + 1024;
-    void (*kern)(CUtensorMap, CUtensorMap, bf16*, int, int, int, int, int*) =
+    void (*kern)(CUtensorMap, CUtensorMap, bf16*, int, int, int, int, ActConsts, int*) =
         epi == EPI_GATED ? gemm_tcgen05_2cta_kernel<EPI_GATED> : gemm_tcgen05_2cta_kernel<EPI_NONE>;
     static bool configured[2] = {false, false};
     static int max_pairs = 0;
@@ -370,6 +370,6 @@ QNN_API int qnn_gemm_tcgen05_2cta(const void* A, const void* B, void* C, int M, 
     const int pairs = ntiles < max_pairs ? (int)ntiles : max_pairs;
     cfg.gridDim = dim3(2 * pairs);
     cfg.numAttrs = (qnn::pdl_enabled() && 2ll * pairs <= qnn::pdl_max_grid()) ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_a, map_b, (bf16*)C, M, N, K, act, status);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_a, map_b, (bf16*)C, M, N, K, act, ActConsts{act_a, act_b}, status);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }

@@ -25,6 +25,7 @@ EPI_NONE, EPI_SOFTCAP, EPI_GATED = 0, 1, 2
 EPI_ACT = 5                  # act(x w^T) without a gate; the launchers get it as epilogue "none" with the code below
 ACT_ALONE = 16               # added to an activation's code: the product's epilogue applies it to the plain product
 ACT_CODES = {"gelu_tanh": 0, "silu": 1, "relu2": 2}
+ACT_XIELU = 3                # an activation with two constants of its own (``act_consts``); never a gate
 SKINNY_MAX_ROWS = 64
 
 
@@ -333,9 +334,10 @@ GEMM_2CTA = os.environ.get("QNN_GEMM_2CTA", "1") != "0"
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, activation: str = "gelu_tanh",
-                 pair: Optional[bool] = None, out: Optional[torch.Tensor] = None):
+                 pair: Optional[bool] = None, out: Optional[torch.Tensor] = None, act_consts=(0.0, 0.0)):
     """x w^T for whole prompts on the 5th-generation tensor cores (bfloat16, any M; K a multiple of 8).
-    Epilogues: none, or gated (w = [gate; up] stacked).  With more than 128 rows pairs of CTAs
+    Epilogues: none, gated (w = [gate; up] stacked), or an activation alone (``"xielu"`` with its two
+    constants in ``act_consts``).  With more than 128 rows pairs of CTAs
     compute 256 x 256 tiles (``pair``; QNN_GEMM_2CTA=0 keeps one CTA per tile).  Returns None when
     the sizes are refused."""
     _req(x, "x", torch.bfloat16, 2)
@@ -344,7 +346,10 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, 
     N = w.shape[0]
     if epilogue not in (EPI_NONE, EPI_GATED, EPI_ACT) or K % 8 or w.shape[1] != K:
         return None
-    act_code = ACT_CODES[activation] + (ACT_ALONE if epilogue == EPI_ACT else 0)
+    if activation == "xielu" and epilogue != EPI_ACT:
+        raise ValueError("gemm_tcgen05: xielu is an activation without a gate")
+    act_code = (ACT_XIELU if activation == "xielu" else ACT_CODES[activation]) + (ACT_ALONE if epilogue == EPI_ACT else 0)
+    ka, kb = float(act_consts[0]), float(act_consts[1])
     if epilogue == EPI_ACT:
         epilogue = EPI_NONE
     n_out = N // 2 if epilogue == EPI_GATED else N
@@ -358,12 +363,12 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, 
     if pair is None:
         pair = GEMM_2CTA and M > 128
     if pair:
-        code = L.qnn_gemm_tcgen05_2cta(_p(x), _p(w), _p(out), M, N, K, epilogue, act_code,
+        code = L.qnn_gemm_tcgen05_2cta(_p(x), _p(w), _p(out), M, N, K, epilogue, act_code, ka, kb,
                                        _p(_status_word(x.device)), _stream())
         if code != _lib.ERR_UNSUPPORTED:
             _lib.check(code, "gemm_tcgen05_2cta")
             return out
-    code = L.qnn_gemm_tcgen05(_p(x), _p(w), _p(out), M, N, K, epilogue, act_code,
+    code = L.qnn_gemm_tcgen05(_p(x), _p(w), _p(out), M, N, K, epilogue, act_code, ka, kb,
                               _p(_status_word(x.device)), _stream())
     if code == _lib.ERR_UNSUPPORTED:
         return None
@@ -451,7 +456,7 @@ def _rows_for_the_small_kernel(M: int, n_out: int, K: int, epilogue: int, device
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: Optional[float] = None,
-           activation: str = "gelu_tanh", out_dtype: Optional[torch.dtype] = None):
+           activation: str = "gelu_tanh", out_dtype: Optional[torch.dtype] = None, act_consts=None):
     """y = x w^T with an optional epilogue.  x: [M, K]; w: [N, K] (gated: [2*N_out, K]).
 
     float32: FFMA kernels only.  bfloat16: the tensor-core small-M kernel up to 64 rows (the cluster
@@ -469,6 +474,16 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
     n_out = N // 2 if epilogue == EPI_GATED else N
     if out_dtype is None:
         out_dtype = torch.float32 if epilogue == EPI_SOFTCAP else x.dtype
+    if activation == "xielu":
+        # the tcgen05 kernels for whole prompts apply it in their epilogue; the kernels for few rows and float32 take
+        # the product and then the activation's own kernel
+        if epilogue != EPI_ACT or act_consts is None:
+            raise ValueError("linear: xielu is an activation without a gate and comes with its two constants")
+        if x.dtype == torch.bfloat16 and M > SKINNY_MAX_ROWS and K % 8 == 0 and USE_TCGEN05 and out_dtype == torch.bfloat16:
+            y = gemm_tcgen05(x, w, epilogue=EPI_ACT, activation="xielu", act_consts=act_consts)
+            if y is not None:
+                return y
+        return xielu_(linear(x, w, out_dtype=out_dtype), act_consts[0], act_consts[1])
     if epilogue == EPI_ACT and (x.dtype == torch.float32 or K % 8 or not USE_TCGEN05 or out_dtype != torch.bfloat16):
         # act(x w^T) where the product's kernels have no such epilogue: the product, then the activation
         return activation_(linear(x, w, out_dtype=out_dtype), activation)

@@ -93,5 +93,7 @@ class MLP(FeedForward):
 
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
         if self.activation == "xielu":
-            return project(ops.xielu_(project(x, self.w_up), *self.xielu), self.w_down)
+            # the product kernels for whole prompts apply it in their epilogue, with its two constants
+            return project(project(x, self.w_up, epilogue=ops.EPI_ACT, activation="xielu", act_consts=self.xielu),
+                           self.w_down)
         return project(project(x, self.w_up, epilogue=ops.EPI_ACT, activation=self.activation), self.w_down)

@@ -16,13 +16,15 @@ def stack_rows(ws: Sequence[torch.Tensor]) -> torch.Tensor:
 
 
 def project(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = ops.EPI_NONE, cap: Optional[float] = None,
-            activation: str = "gelu_tanh", out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+            activation: str = "gelu_tanh", out_dtype: Optional[torch.dtype] = None, act_consts=None) -> torch.Tensor:
     """x w^T.  A matrix that was stored in 32-bit is multiplied in 32-bit even when the
     activations are bfloat16: x is widened, the result narrowed again."""
     if w.dtype == x.dtype:
-        return ops.linear(x, w, epilogue=epilogue, cap=cap, activation=activation, out_dtype=out_dtype)
+        return ops.linear(x, w, epilogue=epilogue, cap=cap, activation=activation, out_dtype=out_dtype,
+                          act_consts=act_consts)
     if w.dtype == torch.float32 and x.dtype == torch.bfloat16:
-        y = ops.linear(ops.cast(x, torch.float32), w, epilogue=epilogue, cap=cap, activation=activation)
+        y = ops.linear(ops.cast(x, torch.float32), w, epilogue=epilogue, cap=cap, activation=activation,
+                       act_consts=act_consts)
         want = out_dtype or (torch.float32 if epilogue == ops.EPI_SOFTCAP else x.dtype)
         return ops.cast(y, want)
     if w.dtype == torch.bfloat16 and x.dtype == torch.float32:

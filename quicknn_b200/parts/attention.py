@@ -129,6 +129,7 @@ class AttentionMixer(Mixer):
             if self.has_bias:
                 biases += [self._carried(tensors["k_bias"], self.n_kv, kd), self._carried(tensors["v_bias"], self.n_kv, vd)]
         self.w_qkv = stack_rows(parts)
+        self.w_qkvg = None
         w_o = tensors["o_proj"]
         if vd != D:                                          # zero columns where the carried values are zero
             wide = torch.zeros((w_o.shape[0], self.n_heads, D), dtype=w_o.dtype, device=w_o.device)
@@ -138,6 +139,13 @@ class AttentionMixer(Mixer):
         self.out_bias = tensors["o_bias"].contiguous() if self.has_bias else None
         if self.out_gate:                                    # zero rows where the carried values are zero
             self.w_out_gate = self._carried(tensors["g_proj"], self.n_heads, vd).contiguous()
+            if self.w_out_gate.dtype == self.w_qkv.dtype:
+                # one matrix q | k | v | g, of which the two above are the row ranges: a decode step forms all four in one
+                # product (its kernels take rows wider than what they read), a prompt keeps two, since the prompt
+                # attention wants its rows packed
+                self.w_qkvg = stack_rows([self.w_qkv, self.w_out_gate])
+                n = self.w_qkv.shape[0]
+                self.w_qkv, self.w_out_gate = self.w_qkvg[:n], self.w_qkvg[n:]
         if self._slope_values is not None:
             self.slopes = torch.tensor(self._slope_values, dtype=torch.float32, device=device)
         if self.has_bias or self.qk_norm:
@@ -223,8 +231,12 @@ class AttentionMixer(Mixer):
         extend = step.mode == "extend"
         fusable = not extend and self.prep is None and not self.shared_kv
         qkv = self.position.project_and_place(x, self.w_qkv, h, step, line) if fusable else None
+        gate_col = 0
         if qkv is None:
-            qkv = project(x, self.w_qkv)
+            if self.w_qkvg is not None and step.mode == "decode":
+                qkv, gate_col = project(x, self.w_qkvg), self.w_qkv.shape[0]
+            else:
+                qkv = project(x, self.w_qkv)
             if self.prep is None:
                 self.position.place(qkv, h, step, line, append=not extend)
             else:
@@ -232,7 +244,9 @@ class AttentionMixer(Mixer):
         if line.has_readers and line.writes and not self.shared_kv and step.mode != "decode":
             step.shared_rows[line.index] = (qkv, h)          # for the layers that read this line later in the step
         a = self.attend(qkv, step, line)
-        if self.out_gate:
+        if gate_col:
+            a = ops.sigmoid_gate_(a, qkv, gate_col)
+        elif self.out_gate:
             a = ops.sigmoid_gate_(a, project(x, self.w_out_gate))
         y = project(a, self.w_o)
         return y if (self.out_bias is None or self.defer_out_bias) else ops.add_bias_(y, self.out_bias)

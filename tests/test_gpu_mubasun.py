@@ -334,13 +334,15 @@ def _clear_choices(x, w, r, margin):
 @pytest.mark.parametrize("W,mlp,rows", [
     (48, _moe(24, 5, 1, 2, 1.7, shared=40), 70), (64, _moe(16, 3, 2, 3, 0.8), 33), (100, _moe(36, 2, 3, 2, 3.0, shared=20), 9),
     (128, _moe(64, 6, 0, 1, 1.0, shared=96), 300), (40, _moe(12, 3, 1, 4, 0.5), 17), (64, _moe(32, 16, 2, 4, 2.5, shared=8), 1),
-    (256, _moe(128, 8, 1, 2, 1.0, shared=64), 700)])
+    (256, _moe(128, 8, 1, 2, 1.0, shared=64), 700), (96, _moe(8, 40, 3, 6, 1.2, shared=16), 150),
+    (64, _moe(16, 70, 0, 16, 0.7), 40)])
 def test_routed_experts_with_identity_experts_and_a_gated_shared_expert(dtype, W, mlp, rows):
     part, w = _routed_part(W, mlp, dtype, 40)
     x = bf(rnd((rows, W), 5))
     want = MP.routed(x.astype(np.float64), w, mlp)
     got = host(part.forward(dev(x, dtype), None))
-    clear = _clear_choices(x.astype(np.float64), w, mlp["router"], 1e-6 if dtype == torch.float32 else 3e-3)
+    n_out = mlp["router"]["experts"] + mlp["router"]["identity"]          # scores are about 1 / n_out: so is a margin
+    clear = _clear_choices(x.astype(np.float64), w, mlp["router"], (1e-6 if dtype == torch.float32 else 3e-3) * 8 / max(8, n_out))
     assert clear.mean() > 0.7
     tol = (3e-5 if dtype == torch.float32 else 0.03) * np.abs(want).max()
     assert np.abs(got - want)[clear].max() < tol
@@ -423,9 +425,10 @@ def test_the_slopes_fall_by_a_constant_factor_down_to_one_in_256():
 @pytest.mark.parametrize("dtype,H,G,d,dv,window", [
     (torch.float32, 4, 2, 16, 24, None), (torch.float32, 2, 1, 24, 8, 9), (torch.float32, 4, 4, 12, 20, 64),
     (torch.float32, 6, 2, 20, 12, 65), (torch.float32, 1, 1, 64, 64, 1), (torch.float32, 4, 2, 32, 32, 63),
-    (torch.float32, 3, 1, 8, 8, 140),
+    (torch.float32, 3, 1, 8, 8, 140), (torch.float32, 8, 1, 16, 16, 20), (torch.float32, 12, 2, 8, 12, None),
     (torch.bfloat16, 4, 1, 64, 40, None), (torch.bfloat16, 4, 2, 64, 64, 70), (torch.bfloat16, 2, 1, 96, 80, 44),
-    (torch.bfloat16, 8, 4, 128, 64, 130), (torch.bfloat16, 4, 2, 24, 40, 7), (torch.bfloat16, 4, 1, 64, 64, 137)])
+    (torch.bfloat16, 8, 4, 128, 64, 130), (torch.bfloat16, 4, 2, 24, 40, 7), (torch.bfloat16, 4, 1, 64, 64, 137),
+    (torch.bfloat16, 16, 2, 64, 64, 100), (torch.bfloat16, 6, 1, 128, 128, None)])
 def test_attention_alone_and_a_window_or_a_slope_one_off_would_show(dtype, H, G, d, dv, window):
     """A prompt longer than the window and two pages, then 70 tokens one by one across a page edge and the ring, then
     a portion.  In float32 the scores are scaled until attention is nearly one-hot, so that a window one token off, a

@@ -288,7 +288,7 @@ def design_sizes(name, design="fuposun"):
     if design == "mubasun":
         matt = {"heads": heads, "kv_heads": kvh, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window}}
         mmoe = {"kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4},
-                "router": {"experts": 16, "identity": 2, "top": 2, "scale": 2.5}}
+                "router": {"experts": 16, "identity": 1, "top": 2, "scale": 1.5}}
         mlayers = []
         for i in range(layers):
             mixer = matt if i % 4 < 2 else dict(matt, kv_from=i - 2)

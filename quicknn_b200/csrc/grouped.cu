@@ -13,6 +13,8 @@
 // Sums are float32; a group's sum is formed by the same threads in the same order whatever else the batch holds.
 #include "common.cuh"
 
+#include <initializer_list>
+
 using namespace qnn;
 
 namespace {
@@ -28,10 +30,13 @@ __device__ __forceinline__ int warps_per_group(int groups) {
 }
 
 // The grouped norm of row[0 .. H) (float32, in global or shared memory; every thread sees what it needs of it):
-// teams of `wpg` warps take the groups in turn.  red: NORM_WARPS floats of shared memory.
+// teams of `wpg` warps take the groups in turn.  red: NORM_WARPS floats of shared memory.  VEC: a thread takes eight
+// consecutive columns at a time with 16-byte accesses (groups of whole eights, every base on 16 bytes).
+template <bool VEC>
 __device__ __forceinline__ void group_norm_row(const float* row, int H, int groups, const void* __restrict__ w, int w_dt,
                                                float eps, void* __restrict__ out, int out_dt, size_t out_base,
                                                float* red) {
+    constexpr int STEP = VEC ? 8 : 1;
     const int gs = H / groups;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wpg = warps_per_group(groups), teams = NORM_WARPS / wpg;
@@ -41,9 +46,15 @@ __device__ __forceinline__ void group_norm_row(const float* row, int H, int grou
         const bool live = g < groups;
         float ss = 0.f;
         if (live)
-            for (int i = in_team; i < gs; i += team_threads) {
-                const float v = row[(size_t)g * gs + i];
-                ss += v * v;
+            for (int i = in_team * STEP; i < gs; i += team_threads * STEP) {
+                if (VEC) {
+                    const float4 a = *reinterpret_cast<const float4*>(row + (size_t)g * gs + i);
+                    const float4 b = *reinterpret_cast<const float4*>(row + (size_t)g * gs + i + 4);
+                    ss += (a.x * a.x + a.y * a.y) + (a.z * a.z + a.w * a.w) + (b.x * b.x + b.y * b.y) + (b.z * b.z + b.w * b.w);
+                } else {
+                    const float v = row[(size_t)g * gs + i];
+                    ss += v * v;
+                }
             }
         ss = warp_sum(ss);
         if (wpg > 1) {
@@ -55,70 +66,135 @@ __device__ __forceinline__ void group_norm_row(const float* row, int H, int grou
         }
         if (live) {
             const float inv = rsqrtf(ss / (float)gs + eps);
-            for (int i = in_team; i < gs; i += team_threads) {
+            for (int i = in_team * STEP; i < gs; i += team_threads * STEP) {
                 const size_t c = (size_t)g * gs + i;
-                store_from_f(out, out_dt, out_base + c, row[c] * inv * load_as_f(w, w_dt, c));
+                if (VEC) {
+                    float wv[8], o[8];
+                    load8_as_f(w, w_dt, c, wv);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] = row[c + e] * inv * wv[e];
+                    store8_from_f(out, out_dt, out_base + c, o);
+                } else {
+                    store_from_f(out, out_dt, out_base + c, row[c] * inv * load_as_f(w, w_dt, c));
+                }
             }
         }
     }
 }
 
+template <bool VEC>
 __global__ void __launch_bounds__(NORM_THREADS)
 group_rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ w, int w_dt, float eps, int groups,
                      void* __restrict__ out, int out_dt, int H) {
-    extern __shared__ float row[];                  // [H], then NORM_WARPS
+    extern __shared__ __align__(16) float row[];    // [H], then NORM_WARPS
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = load_as_f(x, x_dt, base + i);
+    if (VEC) {
+        for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) load8_as_f(x, x_dt, base + i, row + i);
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) row[i] = load_as_f(x, x_dt, base + i);
+    }
     __syncthreads();
-    group_norm_row(row, H, groups, w, w_dt, eps, out, out_dt, base, row + H);
+    group_norm_row<VEC>(row, H, groups, w, w_dt, eps, out, out_dt, base, row + H);
 }
 
+template <bool VEC>
 __global__ void __launch_bounds__(NORM_THREADS)
 add2_group_rmsnorm_kernel(float* __restrict__ resid, const void* __restrict__ a, int a_dt, const void* __restrict__ b,
                           int b_dt, const void* __restrict__ w, int w_dt, float eps, int groups, void* __restrict__ out,
                           int out_dt, int H) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float y = a != nullptr ? load_as_f(a, a_dt, base + i) : 0.f;
-        if (b != nullptr) y += load_as_f(b, b_dt, base + i);
-        const float v = resid[base + i] + y;               // the sublayers' sum first, then the stream
-        resid[base + i] = v;
-        row[i] = v;
+    if (VEC) {
+        for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+            float y[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, z[8], r[8];
+            if (a != nullptr) load8_as_f(a, a_dt, base + i, y);
+            if (b != nullptr) {
+                load8_as_f(b, b_dt, base + i, z);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) y[e] += z[e];
+            }
+            load8_as_f(resid, QNN_DT_F32, base + i, r);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) r[e] += y[e];          // the sublayers' sum first, then the stream
+            store8_from_f(resid, QNN_DT_F32, base + i, r);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) row[i + e] = r[e];
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float y = a != nullptr ? load_as_f(a, a_dt, base + i) : 0.f;
+            if (b != nullptr) y += load_as_f(b, b_dt, base + i);
+            const float v = resid[base + i] + y;               // the sublayers' sum first, then the stream
+            resid[base + i] = v;
+            row[i] = v;
+        }
     }
     if (out == nullptr) return;
     __syncthreads();
-    group_norm_row(row, H, groups, w, w_dt, eps, out, out_dt, base, row + H);
+    group_norm_row<VEC>(row, H, groups, w, w_dt, eps, out, out_dt, base, row + H);
 }
 
+template <bool VEC>
 __global__ void __launch_bounds__(NORM_THREADS)
 embed_pos_kernel(const int* __restrict__ tokens, const void* __restrict__ table, int t_dt, float scale,
                  const void* __restrict__ pos_table, int p_dt, const int* __restrict__ tok_pos, int n_pos,
                  float* __restrict__ out, const void* __restrict__ w, int w_dt, float eps, int groups,
                  void* __restrict__ normed, int n_dt, int H, int V) {
-    extern __shared__ float row[];
+    extern __shared__ __align__(16) float row[];
     pdl_wait();
     const int t = blockIdx.x;
     const int tok = tokens[t], p = tok_pos[t];
     const bool tv = tok >= 0 && tok < V, pv = p >= 0 && p < n_pos;
     const size_t base = (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float v = tv ? load_as_f(table, t_dt, (size_t)tok * H + i) * scale : 0.f;
-        if (pv) v += load_as_f(pos_table, p_dt, (size_t)p * H + i);
-        out[base + i] = v;
-        row[i] = v;
+    if (VEC) {
+        for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, z[8];
+            if (tv) {
+                load8_as_f(table, t_dt, (size_t)tok * H + i, v);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] *= scale;
+            }
+            if (pv) {
+                load8_as_f(pos_table, p_dt, (size_t)p * H + i, z);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] += z[e];
+            }
+            store8_from_f(out, QNN_DT_F32, base + i, v);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) row[i + e] = v[e];
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float v = tv ? load_as_f(table, t_dt, (size_t)tok * H + i) * scale : 0.f;
+            if (pv) v += load_as_f(pos_table, p_dt, (size_t)p * H + i);
+            out[base + i] = v;
+            row[i] = v;
+        }
     }
     if (normed == nullptr) return;
     __syncthreads();
-    group_norm_row(row, H, groups, w, w_dt, eps, normed, n_dt, base, row + H);
+    group_norm_row<VEC>(row, H, groups, w, w_dt, eps, normed, n_dt, base, row + H);
 }
 
+template <bool VEC>
 __global__ void sigmoid_gate_kernel(void* __restrict__ o, int o_dt, long long ldo, const void* __restrict__ g, int g_dt,
                                     long long ldg, int N, int accurate) {
     pdl_wait();
     const size_t ob = (size_t)blockIdx.x * ldo, gb = (size_t)blockIdx.x * ldg;
+    if (VEC) {
+        for (int i = threadIdx.x * 8; i < N; i += blockDim.x * 8) {
+            float z[8], v[8];
+            load8_as_f(g, g_dt, gb + i, z);
+            load8_as_f(o, o_dt, ob + i, v);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                v[e] *= accurate ? 1.f / (1.f + expf(-z[e])) : __fdividef(1.f, 1.f + __expf(-z[e]));
+            store8_from_f(o, o_dt, ob + i, v);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < N; i += blockDim.x) {
         const float z = load_as_f(g, g_dt, gb + i);
         const float s = accurate ? 1.f / (1.f + expf(-z)) : __fdividef(1.f, 1.f + __expf(-z));
@@ -139,6 +215,14 @@ static size_t norm_smem(int H) { return ((size_t)H + NORM_WARPS) * sizeof(float)
 
 // A row is held in shared memory as float32: rows beyond 48 KB need the kernel's limit raised, rows beyond what an SM
 // has are refused.
+// Eight columns at a time: rows and groups of whole eights, every base on 16 bytes (null pointers pass).
+static bool eights(int H, int groups, std::initializer_list<const void*> ps) {
+    if (H % 8 || groups < 1 || (H / groups) % 8) return false;
+    for (const void* p : ps)
+        if (((uintptr_t)p & 15) != 0) return false;
+    return true;
+}
+
 template <typename K>
 static bool row_fits(K kernel, int H) {
     const size_t need = norm_smem(H);
@@ -151,9 +235,9 @@ QNN_API int qnn_group_rmsnorm(const void* x, int x_dt, const void* w, int w_dt, 
                               int out_dt, int T, int H, cudaStream_t st) {
     if (T <= 0) return 0;
     if (groups < 1 || H % groups) return QNN_ERR_ARGUMENT;
-    if (!row_fits(group_rmsnorm_kernel, H)) return QNN_ERR_UNSUPPORTED;
-    launch_pdl(group_rmsnorm_kernel, dim3(T), dim3(NORM_THREADS), norm_smem(H), st, x, x_dt, w, w_dt, eps, groups, out, out_dt,
-               H);
+    auto kern = eights(H, groups, {x, w, out}) ? group_rmsnorm_kernel<true> : group_rmsnorm_kernel<false>;
+    if (!row_fits(kern, H)) return QNN_ERR_UNSUPPORTED;
+    launch_pdl(kern, dim3(T), dim3(NORM_THREADS), norm_smem(H), st, x, x_dt, w, w_dt, eps, groups, out, out_dt, H);
     QNN_LAUNCH_CHECK();
 }
 
@@ -162,9 +246,12 @@ QNN_API int qnn_add2_group_rmsnorm(float* resid, const void* a, int a_dt, const 
                                    float eps, int groups, void* out, int out_dt, int T, int H, cudaStream_t st) {
     if (T <= 0) return 0;
     if (out != nullptr && (groups < 1 || H % groups || w == nullptr)) return QNN_ERR_ARGUMENT;
-    if (!row_fits(add2_group_rmsnorm_kernel, H)) return QNN_ERR_UNSUPPORTED;
-    launch_pdl(add2_group_rmsnorm_kernel, dim3(T), dim3(NORM_THREADS), norm_smem(H), st, resid, a, a_dt, b, b_dt, w, w_dt, eps,
-               groups < 1 ? 1 : groups, out, out_dt, H);
+    if (groups < 1) groups = 1;
+    auto kern = eights(H, out != nullptr ? groups : 1, {resid, a, b, w, out}) ? add2_group_rmsnorm_kernel<true>
+                                                                             : add2_group_rmsnorm_kernel<false>;
+    if (!row_fits(kern, H)) return QNN_ERR_UNSUPPORTED;
+    launch_pdl(kern, dim3(T), dim3(NORM_THREADS), norm_smem(H), st, resid, a, a_dt, b, b_dt, w, w_dt, eps, groups, out, out_dt,
+               H);
     QNN_LAUNCH_CHECK();
 }
 
@@ -174,9 +261,12 @@ QNN_API int qnn_embed_pos(const int* tokens, const void* table, int t_dt, float 
                           void* normed, int n_dt, int T, int H, int V, cudaStream_t st) {
     if (T <= 0) return 0;
     if (normed != nullptr && (groups < 1 || H % groups || w == nullptr)) return QNN_ERR_ARGUMENT;
-    if (!row_fits(embed_pos_kernel, H)) return QNN_ERR_UNSUPPORTED;
-    launch_pdl(embed_pos_kernel, dim3(T), dim3(NORM_THREADS), norm_smem(H), st, tokens, table, t_dt, scale, pos_table, p_dt,
-               tok_pos, n_pos, out, w, w_dt, eps, groups < 1 ? 1 : groups, normed, n_dt, H, V);
+    if (groups < 1) groups = 1;
+    auto kern = eights(H, normed != nullptr ? groups : 1, {table, pos_table, out, w, normed}) ? embed_pos_kernel<true>
+                                                                                               : embed_pos_kernel<false>;
+    if (!row_fits(kern, H)) return QNN_ERR_UNSUPPORTED;
+    launch_pdl(kern, dim3(T), dim3(NORM_THREADS), norm_smem(H), st, tokens, table, t_dt, scale, pos_table, p_dt, tok_pos, n_pos,
+               out, w, w_dt, eps, groups, normed, n_dt, H, V);
     QNN_LAUNCH_CHECK();
 }
 
@@ -186,9 +276,10 @@ QNN_API int qnn_sigmoid_gate(void* o, int o_dt, long long ldo, const void* g, in
                              cudaStream_t st) {
     if (T <= 0 || N <= 0) return 0;
     if (ldo < N || ldg < N) return QNN_ERR_ARGUMENT;
-    const int threads = N >= 1024 ? 256 : 128;
-    launch_pdl(sigmoid_gate_kernel, dim3(T), dim3(threads), 0, st, o, o_dt, ldo, g, g_dt, ldg, N,
-               (int)(o_dt == QNN_DT_F32 && g_dt == QNN_DT_F32));
+    const bool vec = N % 8 == 0 && ldo % 8 == 0 && ldg % 8 == 0 && (((uintptr_t)o | (uintptr_t)g) & 15) == 0;
+    const int threads = N >= (vec ? 2048 : 1024) ? 256 : 128;
+    launch_pdl(vec ? sigmoid_gate_kernel<true> : sigmoid_gate_kernel<false>, dim3(T), dim3(threads), 0, st, o, o_dt, ldo, g,
+               g_dt, ldg, N, (int)(o_dt == QNN_DT_F32 && g_dt == QNN_DT_F32));
     QNN_LAUNCH_CHECK();
 }
 

@@ -183,7 +183,7 @@ def test_window_gate_whole_norm_and_shared_keys_in_the_plain_attention():
 
 def test_the_plain_router_correction_identity_and_shared_gate():
     rng = np.random.default_rng(4)
-    W, mlp = 6, _moe(5, 3, 2, 2, 2.5, shared=4)
+    W, mlp = 6, _moe(5, 3, 2, 2, 1.75, shared=4)
     w = {"router": rng.normal(size=(5, W)), "correction": np.array([0.0, 0.0, 0.0, 0.0, 10.0]),
          "shared.gate": rng.normal(size=(4, W)), "shared.up": rng.normal(size=(4, W)), "shared.down": rng.normal(size=(W, 4)),
          "shared.sg": rng.normal(size=(1, W))}
@@ -194,7 +194,7 @@ def test_the_plain_router_correction_identity_and_shared_gate():
     z = h @ w["router"].T
     s = np.exp(z) / np.exp(z).sum(-1, keepdims=True)
     assert (chosen[:, 0] == 4).all()                                     # the correction decides the choice ...
-    assert np.allclose(weights[:, 0], 2.5 * s[:, 4])                     # ... but not the weight
+    assert np.allclose(weights[:, 0], 1.75 * s[:, 4])                     # ... but not the weight
     assert np.array_equal(chosen[:, 1], np.argmax(s[:, :4], axis=-1))
     got = MP.routed(h, w, mlp)
     for t in range(9):
@@ -203,7 +203,7 @@ def test_the_plain_router_correction_identity_and_shared_gate():
         want = want + weights[t, 1] * (h[t] if e >= 3 else MP.gated_expert(h[t:t + 1], w, f"e{e}.")[0])
         want = want + MP.gated_expert(h[t:t + 1], w, "shared.")[0] * MP.sigmoid(h[t] @ w["shared.sg"][0])
         assert np.allclose(got[t], want)
-    assert not np.allclose(weights.sum(-1), 2.5)                          # not renormalised
+    assert not np.allclose(weights.sum(-1), 1.75)                          # not renormalised
 
 
 def test_parts_declare_their_parameters_without_a_gpu():

@@ -37,7 +37,10 @@ constexpr int MAX_TOP = 16;
 template <typename TX, typename TW>
 __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict__ wr, int T, int W, int E, int top,
                                  int score_fn, int renorm, const float* __restrict__ correction, float out_scale,
-                                 int* __restrict__ sel_e, float* __restrict__ sel_w) {
+                                 int* __restrict__ sel_e, float* __restrict__ sel_w, int extra,
+                                 float* __restrict__ extra_out) {
+    // The matrix may have `extra` rows behind the experts': their products with the row are written to extra_out
+    // [T, extra] as they are (float32) and take no part in the choice (a gate's logit formed in the same pass).
     extern __shared__ float sc[];                       // [E] logits (then scores), [E] what the experts are ranked by
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
@@ -47,7 +50,7 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict_
     // the warps share the experts; a lane's terms and the order of their sum depend on the width only
     constexpr int VX = Vec16<TX>::N, VW = Vec16<TW>::N, V = VX > VW ? VX : VW;
     const bool vec = (W % V) == 0 && ((((uintptr_t)x | (uintptr_t)wr) & 15) == 0);
-    for (int e = warp; e < E; e += nwarp) {
+    for (int e = warp; e < E + extra; e += nwarp) {
         const TW* wrow = wr + (size_t)e * W;
         float d = 0.f;
         if (vec) {
@@ -64,7 +67,10 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict_
             for (int i = lane; i < W; i += 32) d += to_f(xr[i]) * to_f(wrow[i]);
         }
         d = warp_sum(d);
-        if (lane == 0) s[e] = d;
+        if (lane == 0) {
+            if (e < E) s[e] = d;
+            else extra_out[(size_t)t * extra + (e - E)] = d;
+        }
     }
     __syncthreads();
     if (warp != 0) return;
@@ -474,16 +480,17 @@ __global__ void gated_act_clamped_kernel(const T* __restrict__ gu, T* __restrict
 
 QNN_API int qnn_moe_route(const void* x, int x_dt, const void* w_router, int w_dt, int T, int W, int E, int top,
                           int score_fn, int renorm, const float* correction, float out_scale, int* sel_e, float* sel_w,
-                          cudaStream_t st) {
+                          int extra, float* extra_out, cudaStream_t st) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || top > MAX_TOP || W <= 0) return QNN_ERR_ARGUMENT;
+    if (extra < 0 || (extra > 0 && extra_out == nullptr)) return QNN_ERR_ARGUMENT;
     const int warps = E >= 8 ? 8 : (E >= 4 ? 4 : 2);
     const size_t smem = (size_t)2 * E * sizeof(float);
     if (smem > 48 * 1024) return QNN_ERR_UNSUPPORTED;
     const dim3 grid(T), block(warps * 32);
 #define QNN_ROUTE(TX, TW)                                                                                         \
     launch_pdl(moe_route_kernel<TX, TW>, grid, block, smem, st, (const TX*)x, (const TW*)w_router, T, W, E, top,  \
-               score_fn, renorm, correction, out_scale, sel_e, sel_w)
+               score_fn, renorm, correction, out_scale, sel_e, sel_w, extra, extra_out)
     if (x_dt == QNN_DT_BF16 && w_dt == QNN_DT_BF16) QNN_ROUTE(bf16, bf16);
     else if (x_dt == QNN_DT_BF16) QNN_ROUTE(bf16, float);
     else if (w_dt == QNN_DT_BF16) QNN_ROUTE(float, bf16);

@@ -74,7 +74,8 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_gla_scan_segments": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_float, c_vp, c_vp, c_vp, c_vp,
                               c_vp, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp],
     "qnn_gla_norm_gate": [c_vp, c_ll, c_vp, c_int, c_float, c_vp, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp],
-    "qnn_moe_route": [c_vp, c_int, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_float, c_vp, c_vp, c_vp],
+    "qnn_moe_route": [c_vp, c_int, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_float, c_vp, c_vp, c_int,
+                      c_vp, c_vp],
     "qnn_moe_tile_rows": [c_int, c_int, c_int, c_int, c_int],
     "qnn_moe_max_tiles": [c_int, c_int, c_int],
     "qnn_moe_plan": [c_vp, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp],

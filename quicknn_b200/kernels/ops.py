@@ -1056,15 +1056,18 @@ GATED_CLAMPED = 2            # the gated activation g' * sigmoid(alpha g') * (u'
 
 
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False,
-              correction: Optional[torch.Tensor] = None, scale: float = 1.0):
+              correction: Optional[torch.Tensor] = None, scale: float = 1.0, extra: int = 0):
     """(expert ids int32 [rows*top], scores float32 [rows*top]): the ``top`` best experts of every row by
     score(x w_router^T), logits and scores in float32, ties to the lower index.  With ``correction`` (float32, one per
     expert) the experts are ranked by score + correction and weighted by the score alone.  ``scale`` multiplies the
-    weights (after the renormalisation, if any)."""
+    weights (after the renormalisation, if any).  With ``extra`` = n the matrix has n more rows behind the experts';
+    their products with the rows come back as a third result, float32 [rows, n], and take no part in the choice."""
     _req(x, "x", None, 2)
     _req(w_router, "w_router", None, 2)
     T, W = x.shape
-    E = w_router.shape[0]
+    E = w_router.shape[0] - int(extra)
+    if extra < 0 or E < 1:
+        raise ValueError("moe_route: the extra rows leave no expert")
     if w_router.shape[1] != W:
         raise ValueError("moe_route: the router's inner size differs from the rows'")
     if correction is not None:
@@ -1073,10 +1076,11 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, score: str = "s
             raise ValueError("moe_route: a correction per expert")
     sel_e = torch.empty(T * top, dtype=torch.int32, device=x.device)
     sel_w = torch.empty(T * top, dtype=torch.float32, device=x.device)
+    more = torch.empty((T, int(extra)), dtype=torch.float32, device=x.device) if extra else None
     _lib.check(_lib.load().qnn_moe_route(_p(x), dt_code(x), _p(w_router), dt_code(w_router), T, W, E, int(top),
                                          MOE_SCORES[score], int(renormalize), _p(correction), float(scale), _p(sel_e),
-                                         _p(sel_w), _stream()), "moe_route")
-    return sel_e, sel_w
+                                         _p(sel_w), int(extra), _p(more), _stream()), "moe_route")
+    return (sel_e, sel_w, more) if extra else (sel_e, sel_w)
 
 
 MOE_GROUPED_FROM = 64        # rows per expert (on average) from which prompts take the grouped tcgen05 product

@@ -88,6 +88,7 @@ class RoutedExperts(FeedForward):
             raise ValueError("routed experts: a gate for a shared expert that is not there")
         self.correction: Optional[torch.Tensor] = None
         self.w_shared_gate: Optional[torch.Tensor] = None
+        self.w_router_and_gate: Optional[torch.Tensor] = None
         self.w_router: Optional[torch.Tensor] = None
         self.w_gate_up: Optional[torch.Tensor] = None      # [experts, 2 * ff, width]
         self.w_down: Optional[torch.Tensor] = None         # [experts, width, ff]
@@ -125,6 +126,11 @@ class RoutedExperts(FeedForward):
             self.correction = tensors["correction"].to(torch.float32).contiguous()
         if self.has_shared_gate:
             self.w_shared_gate = tensors["shared_gate"].contiguous()
+            if self.w_shared_gate.dtype == self.w_router.dtype:
+                # the gate's row behind the router's: the router's kernel forms its logit in the same pass
+                both = stack_rows([self.w_router, self.w_shared_gate])
+                n = self.w_router.shape[0]
+                self.w_router_and_gate, self.w_router, self.w_shared_gate = both, both[:n], both[n:]
         if self.shared is not None:
             self.shared.load({k[len("shared."):]: v for k, v in tensors.items() if k.startswith("shared.")},
                              compute_dtype, device)
@@ -135,10 +141,14 @@ class RoutedExperts(FeedForward):
         return n + (self.shared.weight_bytes() if self.shared is not None else 0)
 
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
-        sel_e, sel_w = ops.moe_route(x, self.w_router, self.top, self.score, self.renormalize, self.correction,
-                                     self.route_scale)
+        if self.w_router_and_gate is not None:
+            sel_e, sel_w, gate = ops.moe_route(x, self.w_router_and_gate, self.top, self.score, self.renormalize,
+                                               self.correction, self.route_scale, extra=1)
+        else:
+            sel_e, sel_w = ops.moe_route(x, self.w_router, self.top, self.score, self.renormalize, self.correction,
+                                         self.route_scale)
+            gate = ops.small_linear_f32(x, self.w_shared_gate) if self.has_shared_gate else None
         shared = self.shared.forward(x, step) if self.shared is not None else None
-        gate = ops.small_linear_f32(x, self.w_shared_gate) if self.has_shared_gate else None
         xe = x if x.dtype == self.w_gate_up.dtype else ops.cast(x, self.w_gate_up.dtype)
         act = ops.GATED_CLAMPED if self.activation == "clamped" else ops.ACT_CODES["silu"]
         return ops.moe_experts(xe, sel_e, sel_w, self.top, self.w_gate_up, self.w_down, act, self.limit,

@@ -371,6 +371,20 @@ def test_the_router_ranks_by_corrected_scores_and_weighs_by_the_scores():
     assert sel_e.cpu().numpy().reshape(3, top).tolist() == [[0, 1, 2]] * 3 and np.allclose(host(sel_w), 1.0 / (E + n_id))
 
 
+def test_rows_behind_the_routers_give_their_logits_and_take_no_part_in_the_choice():
+    """The shared expert's gate rides in the router's kernel as one more row of its matrix."""
+    from quicknn_b200.kernels import ops
+    for W, E, top, extra in ((40, 5, 2, 1), (100, 3, 3, 2), (64, 33, 4, 1)):
+        w, x = bf(rnd((E + extra, W), 11, 0.5)), bf(rnd((37, W), 12))
+        corr = rnd(E, 13, 0.05)
+        for dtype in (torch.float32, torch.bfloat16):
+            e0, w0 = ops.moe_route(dev(x, dtype), dev(w[:E], dtype), top, "softmax", False, dev(corr), 1.3)
+            e1, w1, more = ops.moe_route(dev(x, dtype), dev(w, dtype), top, "softmax", False, dev(corr), 1.3, extra=extra)
+            assert torch.equal(e0, e1) and torch.equal(w0, w1)
+            want = x.astype(np.float64) @ w[E:].astype(np.float64).T
+            assert more.shape == (37, extra) and np.abs(host(more) - want).max() < 1e-5 * max(1.0, np.abs(want).max())
+
+
 def test_an_identity_expert_returns_the_row_itself():
     """The corrections put every row on the two identity experts: the output is the row times the sum of their two
     scores times the scale, and no expert's matrices take part (they hold NaN)."""
@@ -790,6 +804,21 @@ def test_layer_sizes_that_take_the_tensor_core_kernels(tmp_path):
     for dtype in ("float32", "bfloat16"):
         folder = make_folder(tmp_path, "L", dtype, False)
         _prompts_then_single_tokens(folder, MP.PlainMubasun(folder), reqs, lens, extra, dtype, 2048, "layer sizes")
+
+
+def test_odd_sizes_everywhere(tmp_path):
+    """A width, head sizes, inner widths and a vocabulary that are odd numbers."""
+    raw = dict(architecture="Mubasun", vocab=131, width=39, max_positions=128, norm={"eps": 1e-5, "groups": 3},
+               initializer_range=0.1,
+               layers=[_layer(_att(3, 1, 5, 7, 0.4, window=11), _dense(45)),
+                       _layer(_att(2, 2, 9, 3, 0.3), _moe(11, 3, 1, 2, 1.1, shared=13)),
+                       _layer(_att(6, 1, 5, 7, 0.25, kv_from=0), _moe(7, 2, 0, 1, 0.9))])
+    CONFIGS["O"] = (raw, 31)
+    lens, extra = [70, 3], 4
+    reqs = prompts("O", [n + extra for n in lens], seed=8)
+    for dtype in ("float32", "bfloat16"):
+        folder = make_folder(tmp_path, "O", dtype, False)
+        _prompts_then_single_tokens(folder, MP.PlainMubasun(folder), reqs, lens, extra, dtype, 512, "odd sizes")
 
 
 # ---- configurations drawn at random ---------------------------------------------------------------------------------

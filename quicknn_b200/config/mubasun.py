@@ -13,16 +13,17 @@ embedded token; a layer norms the stream once and adds the sum of its two sublay
                 "shared": {"ff"} (optional)}
              | null}]}
 
-``attention``: grouped-query softmax attention without biases and without a rotation.  Queries and keys pass an RMS
-norm over their whole projection (all heads at once).  A bias ``slope_h * (i - j)`` is taken off the score of query
-position i and key position j, ``slope_h = 2^(-8 (h + 1) / heads)``; ``mask.size`` is a sliding window (absent: every
-earlier position).  The concatenated heads are multiplied by ``sigmoid(W_g h)`` before the output product.  With
+``attention``: grouped-query softmax attention without biases and without a rotation. Queries and keys pass an RMS
+norm over their whole projection (all heads at once). A penalty ``slope_h * (i - j)`` is subtracted from the score of
+query position i and key position j, ``slope_h = 2^(-8 (h + 1) / heads)``; ``mask.size`` is a sliding window (absent:
+every earlier position). The concatenated heads are multiplied by ``sigmoid(W_g h)`` before the output product. With
 ``kv_from`` the layer has no keys and values and reads those of layer j.
 
-Feed-forwards: ``dense`` is down(xIELU(up(h))) with two learned numbers per layer; ``moe`` is a router (softmax
-over experts and identity experts; the choice adds a learned correction to the scores, the weights are the scores
-times ``router.scale``, not renormalised), experts down(silu(gate(h)) * up(h)), identity experts (the input itself
-times the weight) and a shared expert of the same form whose output is multiplied by sigmoid(w . h).
+Feed-forwards: ``dense`` is down(xIELU(up(h))) with two learned numbers per layer; ``moe`` is a router (softmax over
+experts and identity experts; the choice adds a learned correction to the scores, the weights are the scores times
+``router.scale``, with no renormalisation over the chosen ones), experts down(silu(gate(h)) * up(h)), identity experts
+(an entry that contributes weight * h and owns no parameters) and a shared expert of the same form scaled by
+sigmoid(w . h).
 
 Checkpoint names: ``embed``, ``pos``, ``final.norm``, ``head``; layer i: ``l<i>.norm1``, ``l<i>.mix.q|k|v|g|o``,
 ``l<i>.mix.q.norm``, ``l<i>.mix.k.norm``, ``l<i>.mlp.up|down|act`` or ``l<i>.mlp.router``, ``l<i>.mlp.correction``,

@@ -600,7 +600,7 @@ def attn_prefill(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_
     """Causal (optionally windowed) attention of this step's own rows.  qkv: [T, (nq+2nkv)*hd]
     after rotation; returns [T, nq*hd].  bfloat16 with head sizes 64/128/256 runs on the tensor
     cores when the per-sequence arrays (first row, length) are given; everything else takes the
-    generic kernel.  ``slopes`` (float32, one per query head, optional): ``slope * (i - j)`` is taken off the
+    generic kernel.  ``slopes`` (float32, one per query head, optional): ``slope * (i - j)`` is subtracted from the
     score of query position i and key position j."""
     _req(qkv, "qkv", None, 2)
     _check_slopes(slopes, n_heads)

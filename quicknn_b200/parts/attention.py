@@ -19,7 +19,7 @@ Options beyond that (all off unless the spec gives them):
   ``k_norm`` (shared by the heads), before the rotation.
   With ``"over": "projection"`` it is one norm over the whole query projection (all heads together) and one over the
   whole key projection, with weights of those sizes.
-* ``distance_slopes``: one number per query head; ``slope * (i - j)`` is taken off the score of query position i and
+* ``distance_slopes``: one number per query head; ``slope * (i - j)`` is subtracted from the score of query position i and
   key position j (a bias that grows with the distance, in float32 inside the attention kernels).
 * ``out_gate``: the concatenated heads are multiplied, element by element, by sigmoid(``g_proj`` x) before the output
   product.

@@ -10,7 +10,7 @@ feed-forward that a layer may lack.
 is normed (a layer norm here; any norm unfused).  A mixer's ``out_bias`` and the mean of a ``parallel`` mixer's
 branches are formed inside the kernel that norms and adds.
 
-``parallel``: h = norm(x);  x += mixer(h) + ff(h): one norm, both sublayers read its output, and their sum is
+``parallel``: h = norm(x);  x += mixer(h) + ff(h): a single norm feeds the mixer and the feed-forward alike, and their sum is
 added to the stream (a layer may lack the feed-forward).  With a ``group_rmsnorm`` the add and the next layer's
 norm are one kernel.
 

@@ -11,7 +11,7 @@ limit of its own, may run for every token beside them.  Options: ``activation`` 
 silu(gate) * up instead of the clamped one; no ``limit``); ``correction`` (a learned number per expert that is
 added to the scores for the choice only; the weights are the scores without it); ``route_scale`` (multiplies the
 weights); ``identity`` = n (the router has n more outputs than there are experts; those stand for identity
-experts, whose output is the input itself times the weight, and which have no tensors); ``shared_gate`` (the shared
+experts: such an entry contributes weight * x and owns no parameters); ``shared_gate`` (the shared
 expert's output is multiplied by sigmoid(w . x), one number per token).  Everything from the router to the sum stays on the
 device (no count is read back), so a decode step with routed layers is captured in a CUDA graph like any other.
 """

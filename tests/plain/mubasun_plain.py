@@ -6,10 +6,9 @@ of its position.  A layer norms the stream once and adds the sum of its two subl
     h = N(x);   x <- x + (mixer(h) + ff(h))            N: an RMS norm taken in groups, times a weight
 
 * mixer ``attention``: grouped-query softmax attention.  Queries and keys pass an RMS norm over their whole
-  projection (all heads at once).  No rotation: a position enters only through the bias ``m_h (i - j)`` that is taken
-  off the score of query i and key j, ``m_h = 2^(-8 (h + 1) / heads)``, and through the sliding window
-  ``0 <= i - j < mask.size``.  The concatenated heads are multiplied by ``sigmoid(W_g h)`` before the output matrix.
-  With ``kv_from`` = j the layer uses layer j's keys (after their norm) and values with queries of its own.
+  projection (all heads at once).  Nothing is rotated: score(i, j) = scale q_i . k_j - m_h (i - j) with
+  ``m_h = 2^(-8 (h + 1) / heads)``, over the keys with ``0 <= i - j < mask.size`` (all earlier keys without a mask).  The concatenated heads are multiplied by ``sigmoid(W_g h)`` before the output matrix.
+  ``kv_from`` = j: queries of its own against the normed keys and the values that layer j made.
 * feed-forward ``dense``: ``W_down xielu(W_up h)`` with two learned numbers per layer.
 * feed-forward ``moe``: a softmax router over experts and identity experts; the ``top`` largest of score + correction
   are chosen; an expert's weight is its score times ``router.scale``; experts are ``W_down (silu(W_gate h) * W_up h)``,

@@ -123,7 +123,7 @@ def test_a_random_folder_loads_by_its_config(tmp_path):
 def test_the_slopes_and_the_two_ways_to_write_the_bias():
     assert distance_slopes(4) == (0.25, 0.0625, 0.015625, 0.00390625)
     assert np.allclose(distance_slopes(3), MP.slopes(3)) and len(distance_slopes(1)) == 1 and distance_slopes(1)[0] == 2.0 ** -8
-    # without a sink a softmax row does not care whether slope * (i - j) is taken off or slope * j is added
+    # without a sink a softmax row does not care whether slope * (i - j) is subtracted or slope * j is added
     rng = np.random.default_rng(0)
     s = rng.normal(size=(6, 6))
     i, j = np.arange(6)[:, None], np.arange(6)[None, :]
@@ -203,7 +203,7 @@ def test_the_plain_router_correction_identity_and_shared_gate():
         want = want + weights[t, 1] * (h[t] if e >= 3 else MP.gated_expert(h[t:t + 1], w, f"e{e}.")[0])
         want = want + MP.gated_expert(h[t:t + 1], w, "shared.")[0] * MP.sigmoid(h[t] @ w["shared.sg"][0])
         assert np.allclose(got[t], want)
-    assert not np.allclose(weights.sum(-1), 1.75)                          # not renormalised
+    assert not np.allclose(weights.sum(-1), 1.75)                          # the weights are not rescaled to sum to one
 
 
 def test_parts_declare_their_parameters_without_a_gpu():

@@ -86,7 +86,8 @@ constexpr int skinny_min_blocks() { return (NW == 16 && NT >= 2) ? 2 : (NT >= 4 
 template <int NT, int EPI, int NW>
 __global__ void __launch_bounds__(NW * 32, skinny_min_blocks<NT, NW>()) skinny_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
                                                           void* __restrict__ out, int out_dt, int M, int N, int K,
-                                                          float cap, int act, const RopeEpi rp, int* __restrict__ err) {
+                                                          float cap, int act, const RopeEpi rp, int* __restrict__ err,
+                                                          const ActConsts actk) {
     constexpr int COLS = NT * 8;
     constexpr int THREADS = NW * 32;
     __shared__ float red[NW][16][COLS + 1];
@@ -307,7 +308,7 @@ __global__ void __launch_bounds__(NW * 32, skinny_min_blocks<NT, NW>()) skinny_b
         } else if (EPI == EPI_SOFTCAP || EPI == EPI_ARGMAX) {
             v = softcap(v, cap);
         } else if (EPI == EPI_NONE && act >= QNN_ACT_ALONE) {
-            v = activate_fast(v, act - QNN_ACT_ALONE);       // an activation without a gate
+            v = activate_fast(v, act - QNN_ACT_ALONE, actk); // an activation without a gate
         }
         if constexpr (EPI == EPI_ARGMAX) {
             // the 16 lanes of a half-warp hold the CTA's 16 columns of row m: the largest wins, the lowest
@@ -339,7 +340,8 @@ __global__ void __launch_bounds__(NW * 32, skinny_min_blocks<NT, NW>()) skinny_b
 // least two 32-wide blocks and the partial tiles fit in shared memory.
 template <int EPI>
 static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_dt, int M, int N, int K, float cap, int act,
-                         cudaStream_t st, const RopeEpi rp = RopeEpi(), int* err = nullptr) {
+                         cudaStream_t st, const RopeEpi rp = RopeEpi(), int* err = nullptr,
+                         const ActConsts actk = ActConsts{0.f, 0.f}) {
     const int Nout = (EPI == EPI_GATED) ? N / 2 : N;
     const unsigned blocks = (unsigned)((Nout + 15) / 16);
     const int nt = (M + 7) / 8;
@@ -349,11 +351,11 @@ static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_dt, in
     if (nt == 1 && blocks * 16u < 3000u && kblocks >= 64) nw = 32;
 #define QNN_SK(NTV)                                                                                            \
     if (nw == 32 && NTV == 1)                                                                                  \
-        qnn::launch_pdl(skinny_bf16_kernel<1, EPI, 32>, dim3(blocks), dim3(1024), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp, err);         \
+        qnn::launch_pdl(skinny_bf16_kernel<1, EPI, 32>, dim3(blocks), dim3(1024), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp, err, actk);         \
     else if (nw >= 16 && NTV <= 2)                                                                             \
-        qnn::launch_pdl(skinny_bf16_kernel<(NTV <= 2 ? NTV : 1), EPI, 16>, dim3(blocks), dim3(512), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp, err); \
+        qnn::launch_pdl(skinny_bf16_kernel<(NTV <= 2 ? NTV : 1), EPI, 16>, dim3(blocks), dim3(512), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp, err, actk); \
     else                                                                                                       \
-        qnn::launch_pdl(skinny_bf16_kernel<NTV, EPI, 8>, dim3(blocks), dim3(256), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp, err);         \
+        qnn::launch_pdl(skinny_bf16_kernel<NTV, EPI, 8>, dim3(blocks), dim3(256), 0, st, x, W, out, out_dt, M, N, K, cap, act, rp, err, actk);         \
     break;
     switch (nt) {
         case 1: QNN_SK(1)
@@ -367,13 +369,15 @@ static int launch_skinny(const bf16* x, const bf16* W, void* out, int out_dt, in
 }
 
 QNN_API int qnn_skinny_bf16(const void* x, const void* W, void* out, int out_dt, int M, int N, int K, int epi,
-                            float cap, int act, cudaStream_t st) {
+                            float cap, int act, float act_a, float act_b, cudaStream_t st) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 64 || K % 8 != 0 || K <= 0) return QNN_ERR_UNSUPPORTED;
     if (epi == EPI_GATED && (N % 2)) return QNN_ERR_ARGUMENT;
     if (((uintptr_t)x | (uintptr_t)W) & 15) return QNN_ERR_ARGUMENT;
     switch (epi) {
-        case EPI_NONE: return launch_skinny<EPI_NONE>((const bf16*)x, (const bf16*)W, out, out_dt, M, N, K, cap, act, st);
+        case EPI_NONE:
+            return launch_skinny<EPI_NONE>((const bf16*)x, (const bf16*)W, out, out_dt, M, N, K, cap, act, st, RopeEpi(), nullptr,
+                                           ActConsts{act_a, act_b});
         case EPI_SOFTCAP: return launch_skinny<EPI_SOFTCAP>((const bf16*)x, (const bf16*)W, out, out_dt, M, N, K, cap, act, st);
         case EPI_GATED: return launch_skinny<EPI_GATED>((const bf16*)x, (const bf16*)W, out, out_dt, M, N, K, cap, act, st);
     }

@@ -31,7 +31,7 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_check_finite": [c_vp, c_ll, c_vp, c_vp],
     "qnn_rope_cache_write": [c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp,
                              c_vp, c_int, c_int, c_int, c_vp, c_int, c_vp],
-    "qnn_skinny_bf16": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_vp],
+    "qnn_skinny_bf16": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_vp],
     "qnn_skinny_argmax": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_float, c_vp, c_vp],
     "qnn_skinny_qkv_rope": [c_vp, c_vp, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp,
                             c_int, c_int, c_int, c_vp, c_int, c_vp],

@@ -483,6 +483,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
             y = gemm_tcgen05(x, w, epilogue=EPI_ACT, activation="xielu", act_consts=act_consts)
             if y is not None:
                 return y
+        if (x.dtype == torch.bfloat16 and M <= SKINNY_MAX_ROWS and K % 8 == 0 and out_dtype == torch.bfloat16
+                and not _takes_skinny_tcgen05(M, N, K)):
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)      # the kernel for few rows has it too
+            _lib.check(_lib.load().qnn_skinny_bf16(_p(x), _p(w), _p(out), dt_code(out), M, N, K, EPI_NONE, 0.0,
+                                                   ACT_XIELU + ACT_ALONE, float(act_consts[0]), float(act_consts[1]),
+                                                   _stream()), "skinny_bf16")
+            return out
         return xielu_(linear(x, w, out_dtype=out_dtype), act_consts[0], act_consts[1])
     if epilogue == EPI_ACT and (x.dtype == torch.float32 or K % 8 or not USE_TCGEN05 or out_dtype != torch.bfloat16):
         # act(x w^T) where the product's kernels have no such epilogue: the product, then the activation
@@ -518,7 +525,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, epilogue: int = EPI_NONE, cap: O
         if y is not None:
             return y
     def small(xr: torch.Tensor, out: torch.Tensor) -> None:
-        _lib.check(L.qnn_skinny_bf16(_p(xr), _p(w), _p(out), dt_code(out), xr.shape[0], N, K, epilogue, capv, act,
+        _lib.check(L.qnn_skinny_bf16(_p(xr), _p(w), _p(out), dt_code(out), xr.shape[0], N, K, epilogue, capv, act, 0.0, 0.0,
                                      _stream()), "skinny_bf16")
 
     if M <= SKINNY_MAX_ROWS:

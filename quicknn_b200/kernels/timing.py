@@ -71,7 +71,7 @@ def products(args) -> int:
         M, K = x.shape
         N = w.shape[0]
         out = torch.empty((M, N // 2 if epi == ops.EPI_GATED else N), dtype=bf, device=dev)
-        lib.check(L.qnn_skinny_bf16(ops._p(x), ops._p(w), ops._p(out), 1, M, N, K, epi, 0.0, 0, ops._stream()),
+        lib.check(L.qnn_skinny_bf16(ops._p(x), ops._p(w), ops._p(out), 1, M, N, K, epi, 0.0, 0, 0.0, 0.0, ops._stream()),
                   "qnn_skinny_bf16")
         return out
 

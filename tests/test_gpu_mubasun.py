@@ -806,6 +806,23 @@ def test_layer_sizes_that_take_the_tensor_core_kernels(tmp_path):
         _prompts_then_single_tokens(folder, MP.PlainMubasun(folder), reqs, lens, extra, dtype, 2048, "layer sizes")
 
 
+def test_long_prompts_with_windows_that_pass_inside_them_and_over_decoded_tokens(tmp_path):
+    """Prompts of 1200 and 300 tokens, then 40 single tokens: windows of 150 and 300 and a reader without one."""
+    att = _att(6, 2, 32, 32, 0.2, window=150)
+    raw = dict(architecture="Mubasun", vocab=700, width=96, max_positions=1300, norm={"eps": 1e-5, "groups": 3},
+               initializer_range=0.08,
+               layers=[_layer(att, _dense(160)),
+                       _layer(dict(att, kv_from=0, mask={"size": 300}), _moe(48, 6, 1, 2, 1.4, shared=64)),
+                       _layer(_att(4, 1, 64, 64, 0.15), _moe(32, 4, 2, 3, 0.9)),
+                       _layer({k: v for k, v in dict(att, kv_from=0).items() if k != "mask"}, _dense(96))])
+    CONFIGS["F"] = (raw, 41)
+    lens, extra = [1200, 300], 40
+    reqs = prompts("F", [n + extra for n in lens], seed=12)
+    for dtype in ("float32", "bfloat16"):
+        folder = make_folder(tmp_path, "F", dtype, False)
+        _prompts_then_single_tokens(folder, MP.PlainMubasun(folder), reqs, lens, extra, dtype, 4096, "long prompts")
+
+
 def test_odd_sizes_everywhere(tmp_path):
     """A width, head sizes, inner widths and a vocabulary that are odd numbers."""
     raw = dict(architecture="Mubasun", vocab=131, width=39, max_positions=128, norm={"eps": 1e-5, "groups": 3},

@@ -56,7 +56,8 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
                 const float* __restrict__ decay, long long ldd, float q_scale, const int* __restrict__ seq_row0,
                 const int* __restrict__ seq_len, const int* __restrict__ slots, float* __restrict__ state,
                 float* __restrict__ out, long long ldo, int H, int dim, int vdim, int seg_len, int nseg,
-                int decay_per_head, const float* __restrict__ kw, long long ldw, int ones_col, long long state_stride) {
+                int decay_per_head, const float* __restrict__ kw, long long ldw, int ones_col, long long state_stride,
+                int key_from_decay) {
     using C = GlaChunk<RPT, CPT>;
     constexpr int DIMP = RPT * GLA_SHARE;                    // key channels with padding
     constexpr bool AHEAD = RPT <= 16;                        // the next chunk's loads in registers while this one is walked
@@ -102,7 +103,7 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
             if (tt < nt && i < dim) {
                 const size_t row = (size_t)(row0 + t0 + tt);
                 rq[e] = q[row * ld + h * dim + i];
-                rk[e] = k[row * ld + h * dim + i];
+                if (!key_from_decay) rk[e] = k[row * ld + h * dim + i];
                 ra[e] = decay[row * ldd + (decay_per_head ? h : h * dim + i)];
                 if (kw != nullptr) rw[e] = kw[row * ldw + h];
             }
@@ -121,7 +122,9 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
             const int idx = threadIdx.x + e * GLA_THREADS, tt = idx / DIMP, i = idx - tt * DIMP;
             const int at = tt * C::ROW + (i / RPT) * C::PART + (i % RPT);
             buf[at] = to_f(rq[e]) * q_scale;
-            buf[C::ARRAY + at] = to_f(rk[e]) * rw[e];
+            // key_from_decay: the key is what the decay leaves room for, 1 - a, in float32 (rows and channels beyond the
+            // sequence's have a = 1 and so a key of 0)
+            buf[C::ARRAY + at] = (key_from_decay ? 1.f - ra[e] : to_f(rk[e])) * rw[e];
             buf[2 * C::ARRAY + at] = ra[e];
         }
 #pragma unroll
@@ -260,9 +263,9 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, long long ldo
     ss = warp_sum(ss);
     const float inv = rsqrtf(ss / (float)vdim + eps);
     for (int j = lane; j < vdim; j += 32) {
-        const float gv = to_f(g[(size_t)t * ldg + h * vdim + j]);
+        const float gv = gate_act == 2 ? 0.f : to_f(g[(size_t)t * ldg + h * vdim + j]);
         const float wv = w_mode == 0 ? 1.f : load_as_f(w, w_dt, w_mode == 2 ? (size_t)h * vdim + j : (size_t)j);
-        const float ga = gate_act == 1 ? 1.f / (1.f + expf(-gv)) : silu(gv);
+        const float ga = gate_act == 2 ? 1.f : (gate_act == 1 ? 1.f / (1.f + expf(-gv)) : silu(gv));
         out[(size_t)t * ld_out + h * vdim + j] = from_f<T>(orow[j] * scale * inv * wv * ga);
     }
 }
@@ -319,12 +322,36 @@ __global__ void mlstm_gates_kernel(const float* __restrict__ pre, long long ldp,
     if (slot >= 0 && lane == 0) mstate[(size_t)slot * state_stride + h] = m;
 }
 
+// Gates of a matrix memory whose forget gate also decides what is written.  rows: [T, ld] of T with the query columns
+// (nq of them, from column q_col) and the forget gate's pre-activations (nf, from column f_col).  The queries get
+// silu in place; f = l + (1 - l) sigmoid(z + bias), float32, goes to `f_out` [T, nf] (l: a lower bound per channel).
+template <typename T>
+__global__ void bounded_gates_kernel(T* __restrict__ rows, long long ld, int q_col, int nq, int f_col, int nf,
+                                     const void* __restrict__ bias, int b_dt, const void* __restrict__ lower, int l_dt,
+                                     float* __restrict__ f_out, size_t n) {
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t t = i / (size_t)(nq + nf);
+    const int c = (int)(i - t * (size_t)(nq + nf));
+    if (c < nq) {
+        T* at = rows + t * ld + q_col + c;
+        *at = from_f<T>(silu(to_f(*at)));
+    } else {
+        const int j = c - nq;
+        const float z = to_f(rows[t * ld + f_col + j]) + (bias != nullptr ? load_as_f(bias, b_dt, j) : 0.f);
+        const float l = lower != nullptr ? load_as_f(lower, l_dt, j) : 0.f;
+        f_out[t * nf + j] = l + (1.f - l) * (1.f / (1.f + expf(-z)));
+    }
+}
+
 struct ScanExtra {
     int decay_per_head = 0;
     const float* kw = nullptr;
     long long ldw = 0;
     int ones_col = -1;
     long long state_stride = 0;         // 0: H * dim * vdim
+    int key_from_decay = 0;             // the keys are 1 - decay (per key channel), k is not read
 };
 
 template <typename T>
@@ -346,7 +373,7 @@ int scan_launch(const void* q, const void* k, const void* v, long long ld, const
         }                                                                                                            \
         launch_pdl(gla_scan_kernel<T, RPTV, CPTV>, grid, dim3(GLA_THREADS), smem, st, (const T*)q, (const T*)k,     \
                    (const T*)v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, H, dim, vdim,    \
-                   seg_len, nseg, x.decay_per_head, x.kw, x.ldw, x.ones_col, stride);                                \
+                   seg_len, nseg, x.decay_per_head, x.kw, x.ldw, x.ones_col, stride, x.key_from_decay);             \
     }
     if (rpt <= 4) QNN_GLA(4, 4)
     else if (rpt <= 8) QNN_GLA(8, 4)
@@ -386,17 +413,21 @@ int scan_segments(const void* q, const void* k, const void* v, long long ld, con
 // first row and row count of each of the B sequences (both null: sequence b is row b alone); slots: the state slot
 // of each sequence, negative for a row of no sequence (its output is zero, no state is touched); state:
 // [slots, H, dim, vdim] float32; out: [rows, H*vdim] float32.  dim up to 256.
+// key_from_decay != 0: the keys are 1 - decay, formed in float32 as the rows are staged; k is not read (may be null).
 QNN_API int qnn_gla_scan(const void* q, const void* k, const void* v, long long ld, int dtype, const float* decay,
                          long long ldd, float q_scale, const int* seq_row0, const int* seq_len, const int* slots,
-                         float* state, float* out, long long ldo, int B, int H, int dim, int vdim, cudaStream_t st) {
+                         float* state, float* out, long long ldo, int B, int H, int dim, int vdim, int key_from_decay,
+                         cudaStream_t st) {
     if (B <= 0) return 0;
     if (H <= 0 || dim <= 0 || vdim <= 0 || H > 65535 || B > 65535) return QNN_ERR_ARGUMENT;
     if ((seq_row0 == nullptr) != (seq_len == nullptr)) return QNN_ERR_ARGUMENT;
+    ScanExtra x;
+    x.key_from_decay = key_from_decay ? 1 : 0;
     if (dtype == QNN_DT_BF16)
         return scan_launch<bf16>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim,
-                                 vdim, 0, 1, st);
+                                 vdim, 0, 1, st, x);
     return scan_launch<float>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim, vdim,
-                              0, 1, st);
+                              0, 1, st, x);
 }
 
 // The same for sequences of up to nseg * seg_len rows, in segments that run side by side (see above).  scratch:
@@ -404,16 +435,18 @@ QNN_API int qnn_gla_scan(const void* q, const void* k, const void* v, long long 
 QNN_API int qnn_gla_scan_segments(const void* q, const void* k, const void* v, long long ld, int dtype, const float* decay,
                                   long long ldd, float q_scale, const int* seq_row0, const int* seq_len, const int* slots,
                                   float* state, float* out, long long ldo, int B, int H, int dim, int vdim, int seg_len,
-                                  int nseg, float* scratch, float* seg_decay, cudaStream_t st) {
+                                  int nseg, float* scratch, float* seg_decay, int key_from_decay, cudaStream_t st) {
     if (B <= 0) return 0;
     if (H <= 0 || dim <= 0 || vdim <= 0 || H > 65535 || seg_len < 1 || nseg < 1 || (long long)B * nseg > 65535)
         return QNN_ERR_ARGUMENT;
     if (seq_row0 == nullptr || seq_len == nullptr) return QNN_ERR_ARGUMENT;
+    ScanExtra x;
+    x.key_from_decay = key_from_decay ? 1 : 0;
     if (dtype == QNN_DT_BF16)
         return scan_segments<bf16>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim,
-                                   vdim, seg_len, nseg, scratch, seg_decay, st);
+                                   vdim, seg_len, nseg, scratch, seg_decay, st, x);
     return scan_segments<float>(q, k, v, ld, decay, ldd, q_scale, seq_row0, seq_len, slots, state, out, ldo, B, H, dim, vdim,
-                                seg_len, nseg, scratch, seg_decay, st);
+                                seg_len, nseg, scratch, seg_decay, st, x);
 }
 
 // The scan with one decay per (row, head): S_t = d_t S_{t-1} + w_t k_t v_t^T, o_t = S_t^T (q_t q_scale).
@@ -471,6 +504,7 @@ QNN_API int qnn_head_norm_gate(const float* o, long long ldo, int hs, const floa
     if (rows <= 0) return 0;
     if (H <= 0 || vdim <= 0 || hs < vdim || (den != nullptr && hs <= vdim) || (w_mode != 0 && w == nullptr))
         return QNN_ERR_ARGUMENT;
+    if (gate_act < 0 || gate_act > 2 || (gate_act != 2 && g == nullptr)) return QNN_ERR_ARGUMENT;      // 2: no gate
     const int warps = 4;
     const dim3 grid(((size_t)rows * H + warps - 1) / warps);
     if (dtype == QNN_DT_BF16)
@@ -479,6 +513,21 @@ QNN_API int qnn_head_norm_gate(const float* o, long long ldo, int hs, const floa
     else
         launch_pdl(head_norm_gate_kernel<float>, grid, dim3(warps * 32), 0, st, o, ldo, hs, den, ldden, w, w_dt, w_mode, eps,
                    (const float*)g, ldg, gate_act, (float*)out, ld_out, rows, H, vdim);
+    QNN_LAUNCH_CHECK();
+}
+
+QNN_API int qnn_bounded_gates(void* rows, int dtype, long long ld, int T, int q_col, int nq, int f_col, int nf,
+                              const void* bias, int b_dt, const void* lower, int l_dt, float* f_out, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (nq < 0 || nf <= 0 || q_col < 0 || f_col < 0 || f_out == nullptr) return QNN_ERR_ARGUMENT;
+    const size_t n = (size_t)T * (nq + nf);
+    const dim3 grid((unsigned)((n + 255) / 256));
+    if (dtype == QNN_DT_BF16)
+        launch_pdl(bounded_gates_kernel<bf16>, grid, dim3(256), 0, st, (bf16*)rows, ld, q_col, nq, f_col, nf, bias, b_dt,
+                   lower, l_dt, f_out, n);
+    else
+        launch_pdl(bounded_gates_kernel<float>, grid, dim3(256), 0, st, (float*)rows, ld, q_col, nq, f_col, nf, bias, b_dt,
+                   lower, l_dt, f_out, n);
     QNN_LAUNCH_CHECK();
 }
 

@@ -11,12 +11,22 @@
 //      whose inputs must not be rounded again);
 //   5. keys and values appended to a paged cache line (optional; ring aware like qnn_rope_cache_write).
 //
+// `flags` (QNN_PREP_*): WHOLE = the norm of step 2 over all heads together; NORM_LAST = step 2 comes after step 3 (the
+// heads are rotated first and normed then); PLAIN_NORM = the norm has no weights (wq / wk are null); VALUES_ARE_KEYS =
+// the source rows hold no value columns: the values are the keys as they are after step 1, before norm and rotation
+// (the destination gets them behind the keys, the cache line as its values).
+//
 // Everything between load and store is float32.  A block per token, a warp per head; the angles of a token are
 // formed once per block.  inv_freq comes from the host (float64 arithmetic, rounded once), so any rescaling of the
 // frequencies is the caller's business.
 #include "common.cuh"
 
 using namespace qnn;
+
+#define QNN_PREP_WHOLE 1
+#define QNN_PREP_NORM_LAST 2
+#define QNN_PREP_PLAIN_NORM 4
+#define QNN_PREP_VALUES_ARE_KEYS 8
 
 namespace {
 
@@ -27,7 +37,10 @@ __global__ void head_prep_kernel(const T* src, long long lds, void* dst, int dst
                                  const void* __restrict__ wk, int w_dt, float eps, const float* __restrict__ inv_freq,
                                  const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, T* __restrict__ k_pool,
                                  T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages, int page_size,
-                                 int ring, const int* __restrict__ slot_len, int write_cache, int norm_whole) {
+                                 int ring, const int* __restrict__ slot_len, int write_cache, int flags) {
+    const int norm_whole = flags & QNN_PREP_WHOLE;
+    const bool norm_last = flags & QNN_PREP_NORM_LAST, plain = flags & QNN_PREP_PLAIN_NORM;
+    const bool v_is_k = flags & QNN_PREP_VALUES_ARE_KEYS;
     extern __shared__ float sm[];                   // [rot/2] (cos, sin) pairs, a head of hd floats per warp, [nq + nk] sums
     pdl_wait();
     const int t = blockIdx.x;
@@ -88,12 +101,27 @@ __global__ void head_prep_kernel(const T* src, long long lds, void* dst, int dst
             if (c < norm_dim) ss += v * v;
         }
         const void* w = is_k ? wk : wq;
-        if (w != nullptr) {
+        const bool normed = w != nullptr || (plain && norm_dim > 0);
+        if (is_k && v_is_k) {
+            // the values are the keys as they stand here: behind the keys in the destination, and the line's values
+            T* vc = (wr && v_pool != nullptr) ? v_pool + cache_base + (size_t)(h - nq) * head_stride : nullptr;
+            for (int c = lane; c < hd; c += 32) {
+                store_from_f(dst, dst_dt, out_row + (size_t)(h + nk) * hd + c, mine[c]);
+                if (vc != nullptr) vc[c] = from_f<T>(mine[c]);
+            }
+        }
+        auto norm = [&]() {
+            if (norm_last) {                       // the sum of the rotated head's squares
+                ss = 0.f;
+                for (int c = lane; c < norm_dim; c += 32) ss += mine[c] * mine[c];
+            }
             ss = warp_sum(ss);
             const float inv = norm_whole ? (is_k ? inv_k : inv_q) : rsqrtf(ss / (float)norm_dim + eps);
             const size_t w0 = norm_whole ? (size_t)(is_k ? h - nq : h) * norm_dim : 0;
-            for (int c = lane; c < norm_dim; c += 32) mine[c] = mine[c] * inv * load_as_f(w, w_dt, w0 + c);
-        }
+            for (int c = lane; c < norm_dim; c += 32)
+                mine[c] = mine[c] * inv * (w != nullptr ? load_as_f(w, w_dt, w0 + c) : 1.f);
+        };
+        if (normed && !norm_last) norm();
         __syncwarp();
         for (int j = lane; j < rh; j += 32) {
             const int ia = interleaved ? 2 * j : j, ib = interleaved ? 2 * j + 1 : j + rh;
@@ -103,6 +131,10 @@ __global__ void head_prep_kernel(const T* src, long long lds, void* dst, int dst
             mine[ib] = b * cs.x + a * cs.y;
         }
         __syncwarp();
+        if (normed && norm_last) {
+            norm();
+            __syncwarp();
+        }
         T* cache = (is_k && wr) ? k_pool + cache_base + (size_t)(h - nq) * head_stride : nullptr;
         for (int c = lane; c < hd; c += 32) {
             const float v = mine[c];
@@ -114,7 +146,7 @@ __global__ void head_prep_kernel(const T* src, long long lds, void* dst, int dst
     // values: nv columns behind the keys (nv = kv heads x hd when they go to the cache)
     const size_t v0 = (size_t)(nq + nk) * hd;
     const bool v_cache = wr && v_pool != nullptr;
-    if (nv > 0 && (bias != nullptr || v_cache || (const void*)src != (const void*)dst)) {
+    if (nv > 0 && !v_is_k && (bias != nullptr || v_cache || (const void*)src != (const void*)dst)) {
         for (int c = threadIdx.x; c < nv; c += blockDim.x) {
             float v = to_f(row[v0 + c]);
             if (bias != nullptr) v += load_as_f(bias, b_dt, v0 + c);
@@ -133,7 +165,10 @@ __global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, v
                                      const void* __restrict__ wk, int w_dt, float eps, const float* __restrict__ inv_freq,
                                      const int* __restrict__ tok_pos, const int* __restrict__ tok_slot, void* k_pool,
                                      void* v_pool, const int* __restrict__ page_table, int max_pages, int page_size,
-                                     int ring, const int* __restrict__ slot_len, int write_cache, int norm_whole) {
+                                     int ring, const int* __restrict__ slot_len, int write_cache, int flags) {
+    const int norm_whole = flags & QNN_PREP_WHOLE;
+    const bool norm_last = flags & QNN_PREP_NORM_LAST, plain = flags & QNN_PREP_PLAIN_NORM;
+    const bool v_is_k = flags & QNN_PREP_VALUES_ARE_KEYS;
     extern __shared__ float sm[];                   // [rot/2] (cos, sin) pairs, then [nq + nk] sums
     pdl_wait();
     const int t = blockIdx.x;
@@ -202,7 +237,13 @@ __global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, v
             }
         }
         const void* w = is_k ? wk : wq;
-        if (w != nullptr) {
+        const bool normed = w != nullptr || (plain && norm_dim > 0);
+        if (is_k && v_is_k && active) {
+            store8_from_f(dst, d_dt, out_row + (size_t)(h + nk) * hd + col, v);
+            if (wr && v_pool != nullptr)
+                store8_from_f(v_pool, d_dt, cache_base + (size_t)(h - nq) * head_stride + col, v);
+        }
+        auto norm = [&]() {
             float ss = 0.f;
 #pragma unroll
             for (int e = 0; e < 8; ++e)
@@ -212,8 +253,9 @@ __global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, v
             const size_t w0 = norm_whole ? (size_t)(is_k ? h - nq : h) * norm_dim : 0;
 #pragma unroll
             for (int e = 0; e < 8; ++e)
-                if (col + e < norm_dim) v[e] = v[e] * inv * load_as_f(w, w_dt, w0 + col + e);
-        }
+                if (col + e < norm_dim) v[e] = v[e] * inv * (w != nullptr ? load_as_f(w, w_dt, w0 + col + e) : 1.f);
+        };
+        if (normed && !norm_last) norm();
         if (rot > 0) {
             if (interleaved) {
 #pragma unroll
@@ -241,6 +283,7 @@ __global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, v
                 }
             }
         }
+        if (normed && norm_last) norm();
         if (active) {
             store8_from_f(dst, d_dt, out_row + c0 + col, v);
             if (is_k && wr) store8_from_f(k_pool, d_dt, cache_base + (size_t)(h - nq) * head_stride + col, v);
@@ -248,7 +291,7 @@ __global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, v
     }
     const size_t v0 = (size_t)(nq + nk) * hd;
     const bool v_cache = wr && v_pool != nullptr;
-    if (nv > 0 && (bias != nullptr || v_cache || src != (const void*)dst)) {
+    if (nv > 0 && !v_is_k && (bias != nullptr || v_cache || src != (const void*)dst)) {
         for (int c = threadIdx.x * 8; c < nv; c += blockDim.x * 8) {
             float v[8];
             load8_as_f(src, s_dt, in_row + v0 + c, v);
@@ -270,17 +313,24 @@ __global__ void head_prep_vec_kernel(const void* src, int s_dt, long long lds, v
 // order; dst: the same layout with row pitch ldd in `dst_dt` (may be src itself).  bias: over the packed row, or null.
 // wq / wk: norm weights [norm_dim] of `w_dt` (with norm_whole: [nq * norm_dim] and [nk * norm_dim]), or null.  inv_freq: [rot/2] float32.  The cache arguments are those of
 // qnn_rope_cache_write; with write_cache, nv must be nk * hd (or 0 with v_pool null) and dst_dt the pools' type.
+// flags: QNN_PREP_* (see the head of this file).
 QNN_API int qnn_head_prep(const void* src, int dtype, long long lds, void* dst, int dst_dt, long long ldd, int T, int nq,
                           int nk, int nv, int hd, int norm_dim, int rot, int interleaved, const void* bias, int b_dt,
                           const void* wq, const void* wk, int w_dt, float eps, const float* inv_freq, const int* tok_pos,
                           const int* tok_slot, void* k_pool, void* v_pool, const int* page_table, int max_pages,
-                          int page_size, int ring, const int* slot_len, int write_cache, int norm_whole,
+                          int page_size, int ring, const int* slot_len, int write_cache, int flags,
                           cudaStream_t st) {
     if (T <= 0) return 0;
+    const int norm_whole = flags & QNN_PREP_WHOLE;
     if (nq < 0 || nk < 0 || nv < 0 || hd <= 0 || rot % 2 || rot < 0 || rot > hd || norm_dim < 0 || norm_dim > hd)
         return QNN_ERR_ARGUMENT;
     if ((wq != nullptr || wk != nullptr) && norm_dim == 0) return QNN_ERR_ARGUMENT;
     if (norm_whole && ((nq > 0 && wq == nullptr) || (nk > 0 && wk == nullptr))) return QNN_ERR_ARGUMENT;
+    // a norm over all heads is formed before anything else: it cannot come after the rotation, nor go without weights
+    if (norm_whole && (flags & (QNN_PREP_NORM_LAST | QNN_PREP_PLAIN_NORM))) return QNN_ERR_ARGUMENT;
+    if ((flags & QNN_PREP_PLAIN_NORM) && (wq != nullptr || wk != nullptr)) return QNN_ERR_ARGUMENT;
+    // values that are the keys: as many value columns as key columns, in a destination that is not the source
+    if ((flags & QNN_PREP_VALUES_ARE_KEYS) && (nv != nk * hd || src == (const void*)dst)) return QNN_ERR_ARGUMENT;
     if (rot > 0 && (inv_freq == nullptr || tok_pos == nullptr)) return QNN_ERR_ARGUMENT;
     if (write_cache && (tok_slot == nullptr || k_pool == nullptr || page_table == nullptr || slot_len == nullptr ||
                         (v_pool != nullptr && nv != nk * hd)))
@@ -298,7 +348,7 @@ QNN_API int qnn_head_prep(const void* src, int dtype, long long lds, void* dst, 
         launch_pdl(head_prep_vec_kernel, dim3(T), dim3(warps * 32), ((size_t)rot + heads) * sizeof(float), st, src, dtype, lds,
                    dst, dst_dt, ldd, nq, nk, nv, hd, norm_dim, rot, interleaved, bias, b_dt, wq, wk, w_dt, eps, inv_freq,
                    tok_pos, tok_slot, k_pool, v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache,
-                   norm_whole);
+                   flags);
         QNN_LAUNCH_CHECK();
     }
     const size_t smem = ((size_t)rot + (size_t)warps * hd + heads) * sizeof(float);
@@ -306,10 +356,10 @@ QNN_API int qnn_head_prep(const void* src, int dtype, long long lds, void* dst, 
     if (dtype == QNN_DT_BF16)
         launch_pdl(head_prep_kernel<bf16>, dim3(T), dim3(warps * 32), smem, st, (const bf16*)src, lds, dst, dst_dt, ldd, nq, nk,
                    nv, hd, norm_dim, rot, interleaved, bias, b_dt, wq, wk, w_dt, eps, inv_freq, tok_pos, tok_slot,
-                   (bf16*)k_pool, (bf16*)v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache, norm_whole);
+                   (bf16*)k_pool, (bf16*)v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache, flags);
     else
         launch_pdl(head_prep_kernel<float>, dim3(T), dim3(warps * 32), smem, st, (const float*)src, lds, dst, dst_dt, ldd, nq,
                    nk, nv, hd, norm_dim, rot, interleaved, bias, b_dt, wq, wk, w_dt, eps, inv_freq, tok_pos, tok_slot,
-                   (float*)k_pool, (float*)v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache, norm_whole);
+                   (float*)k_pool, (float*)v_pool, page_table, max_pages, page_size, ring, slot_len, write_cache, flags);
     QNN_LAUNCH_CHECK();
 }

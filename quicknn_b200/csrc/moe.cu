@@ -38,10 +38,10 @@ template <typename TX, typename TW>
 __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict__ wr, int T, int W, int E, int top,
                                  int score_fn, int renorm, const float* __restrict__ correction, float out_scale,
                                  int* __restrict__ sel_e, float* __restrict__ sel_w, int extra,
-                                 float* __restrict__ extra_out) {
+                                 float* __restrict__ extra_out, int n_groups, int keep_groups) {
     // The matrix may have `extra` rows behind the experts': their products with the row are written to extra_out
     // [T, extra] as they are (float32) and take no part in the choice (a gate's logit formed in the same pass).
-    extern __shared__ float sc[];                       // [E] logits (then scores), [E] what the experts are ranked by
+    extern __shared__ float sc[];                       // [E] logits (then scores), [E] what the experts are ranked by, [groups]
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
     const int t = blockIdx.x;
@@ -88,13 +88,51 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict_
     // With a correction the experts are ranked by score + correction[e] and weighted by the score alone, so every
     // expert's score is formed first.
     float* rank = s;
-    if (correction != nullptr) {
+    const bool ranked = correction != nullptr || n_groups > 1;
+    if (ranked) {
         rank = s + E;
         for (int e = lane; e < E; e += 32) {
             const float v = score_fn == QNN_MOE_SCORE_SOFTMAX ? expf(s[e] - m) / sum : 1.f / (1.f + expf(-s[e]));
             s[e] = v;
-            rank[e] = v + correction[e];
+            rank[e] = v + (correction != nullptr ? correction[e] : 0.f);
         }
+        __syncwarp();
+    }
+    // Groups of neighbouring experts: a group's score is the sum of its two largest ranking values (of its one, where
+    // a group is a single expert); only the `keep_groups` best groups stay in the ranking (ties to the lower group),
+    // the others' experts rank as minus infinity.
+    if (n_groups > 1 && keep_groups < n_groups) {
+        float* gs = s + 2 * E;
+        const int per = E / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;              // the largest and the second
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = rank[e];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            gs[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        for (int k = 0; k < keep_groups; ++k) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float v = gs[g];
+                if (v > best && v != INFINITY) { best = v; arg = g; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            }
+            __syncwarp();
+            if (lane == 0 && arg != 0x7fffffff) gs[arg] = INFINITY;       // kept
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] != INFINITY) rank[e] = -INFINITY;
         __syncwarp();
     }
     float total = 0.f;
@@ -112,7 +150,7 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict_
             if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
         }
         if (arg == 0x7fffffff) arg = 0;                    // logits that are all NaN: any expert, the model's logits will show it
-        if (correction != nullptr) best = s[arg];
+        if (ranked) best = s[arg];
         else best = score_fn == QNN_MOE_SCORE_SOFTMAX ? expf(best - m) / sum : 1.f / (1.f + expf(-best));
         total += best;
         __syncwarp();
@@ -126,7 +164,7 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const TW* __restrict_
     if (lane == 0 && (renorm || out_scale != 1.f))
         for (int k = 0; k < top; ++k) {
             float w = sel_w[(size_t)t * top + k];
-            if (renorm) w /= total;
+            if (renorm) w /= total + 1e-20f;
             sel_w[(size_t)t * top + k] = w * out_scale;
         }
 }
@@ -183,7 +221,7 @@ __device__ __forceinline__ float gated(float g, float u, int act, float limit, f
 // acc[m][r] += sum_k xs[k][r] * w_m[col][k] over K, for NM matrices whose rows `col` lie `K` apart.
 // xs is filled by `fill(k0, kn)` for each block of inner elements.
 template <typename TW, int NM, typename Fill>
-__device__ __forceinline__ void tile_product(const TW* const (&w)[NM], int col0, int n_cols, int K, float (*xs)[TILE_ROWS],
+__device__ __forceinline__ void tile_product(const TW* const* w, int col0, int n_cols, int K, float (*xs)[TILE_ROWS],
                                              float (*ws)[TILE_K][TILE_COLS + 1], float (&acc)[NM][TILE_ROWS], Fill fill) {
     for (int k0 = 0; k0 < K; k0 += TILE_K) {
         const int kn = min(TILE_K, K - k0);
@@ -214,14 +252,16 @@ __device__ __forceinline__ void tile_product(const TW* const (&w)[NM], int col0,
     }
 }
 
-template <typename T>
+// NM = 2: the expert's matrix holds gate rows, then up rows, and the result is act(gate) * up; NM = 1: up rows alone,
+// and the result is act(up).
+template <typename T, int NM>
 __global__ void __launch_bounds__(TILE_COLS)
 moe_gate_up_kernel(const T* __restrict__ x, int W, const T* __restrict__ w_gu, int ff, const int* __restrict__ offsets,
                    const int* __restrict__ perm, const float* __restrict__ sel_w, const int* __restrict__ tiles,
                    const int* __restrict__ n_tiles, int top, int scale_input, int act, float limit, float alpha,
                    T* __restrict__ hidden) {
     __shared__ __align__(16) float xs[TILE_K][TILE_ROWS];
-    __shared__ float ws[2][TILE_K][TILE_COLS + 1];
+    __shared__ float ws[NM][TILE_K][TILE_COLS + 1];
     __shared__ int src_row[TILE_ROWS];
     __shared__ float src_w[TILE_ROWS];
     pdl_wait();
@@ -234,12 +274,16 @@ moe_gate_up_kernel(const T* __restrict__ x, int W, const T* __restrict__ w_gu, i
         src_row[threadIdx.x] = entry < 0 ? -1 : entry / top;
         src_w[threadIdx.x] = (entry < 0 || !scale_input) ? 1.f : sel_w[entry];
     }
-    const T* wg = w_gu + (size_t)e * 2 * ff * W;
-    const T* const w2[2] = {wg, wg + (size_t)ff * W};
-    float acc[2][TILE_ROWS];
+    const T* wg = w_gu + (size_t)e * NM * ff * W;
+    const T* w2[NM];
 #pragma unroll
-    for (int r = 0; r < TILE_ROWS; ++r) acc[0][r] = acc[1][r] = 0.f;
-    tile_product<T, 2>(w2, col0, n_cols, W, xs, ws, acc, [&](int k0, int kn) {
+    for (int m = 0; m < NM; ++m) w2[m] = wg + (size_t)m * ff * W;
+    float acc[NM][TILE_ROWS];
+#pragma unroll
+    for (int m = 0; m < NM; ++m)
+#pragma unroll
+        for (int r = 0; r < TILE_ROWS; ++r) acc[m][r] = 0.f;
+    tile_product<T, NM>(w2, col0, n_cols, W, xs, ws, acc, [&](int k0, int kn) {
         for (int idx = threadIdx.x; idx < TILE_ROWS * TILE_K; idx += TILE_COLS) {
             const int r = idx / TILE_K, kk = idx - r * TILE_K;
             const int row = src_row[r];
@@ -248,7 +292,8 @@ moe_gate_up_kernel(const T* __restrict__ x, int W, const T* __restrict__ w_gu, i
     });
     if ((int)threadIdx.x < n_cols)
         for (int r = 0; r < rows; ++r)
-            hidden[(size_t)(p0 + r) * ff + col0 + threadIdx.x] = from_f<T>(gated(acc[0][r], acc[1][r], act, limit, alpha));
+            hidden[(size_t)(p0 + r) * ff + col0 + threadIdx.x] =
+                from_f<T>(NM == 2 ? gated(acc[0][r], acc[NM - 1][r], act, limit, alpha) : activate(acc[0][r], act));
 }
 
 template <typename T>
@@ -300,7 +345,7 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 // acc[m][t][j] += rows x weights over K (a multiple of 32) for NM matrices; `fill(k0, kn)` puts the rows' elements
 // k0 .. k0 + kn - 1 into xs ([MT*16][MMA_PITCH] bfloat16, zero rows beyond the tile's).
 template <int MT, int NM, typename Fill>
-__device__ __forceinline__ void mma_tile_product(const bf16* const (&w)[NM], int col0, int n_cols, int K, bf16* xs,
+__device__ __forceinline__ void mma_tile_product(const bf16* const* w, int col0, int n_cols, int K, bf16* xs,
                                                  float (&acc)[NM][MT][MMA_NW][4], Fill fill) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tg = lane & 3;
     const bf16* wrow[NM][MMA_NW];
@@ -346,7 +391,7 @@ __device__ __forceinline__ void mma_tile_product(const bf16* const (&w)[NM], int
     }
 }
 
-template <int MT>
+template <int MT, int NM>
 __global__ void __launch_bounds__(MMA_WARPS * 32)
 moe_gate_up_mma_kernel(const bf16* __restrict__ x, int W, const bf16* __restrict__ w_gu, int ff,
                        const int* __restrict__ offsets, const int* __restrict__ perm, const float* __restrict__ sel_w,
@@ -366,10 +411,12 @@ moe_gate_up_mma_kernel(const bf16* __restrict__ x, int W, const bf16* __restrict
         src_row[r] = entry < 0 ? -1 : entry / top;
         src_w[r] = (entry < 0 || !scale_input) ? 1.f : sel_w[entry];
     }
-    const bf16* wg = w_gu + (size_t)e * 2 * ff * W;
-    const bf16* const w2[2] = {wg, wg + (size_t)ff * W};
-    float acc[2][MT][MMA_NW][4] = {};
-    mma_tile_product<MT, 2>(w2, col0, n_cols, W, xs, acc, [&](int k0, int kn) {
+    const bf16* wg = w_gu + (size_t)e * NM * ff * W;
+    const bf16* w2[NM];
+#pragma unroll
+    for (int m = 0; m < NM; ++m) w2[m] = wg + (size_t)m * ff * W;
+    float acc[NM][MT][MMA_NW][4] = {};
+    mma_tile_product<MT, NM>(w2, col0, n_cols, W, xs, acc, [&](int k0, int kn) {
         for (int idx = threadIdx.x; idx < MT * 16 * (MMA_KC / 8); idx += blockDim.x) {
             const int r = idx / (MMA_KC / 8), kk = (idx - r * (MMA_KC / 8)) * 8;
             const int row = src_row[r];
@@ -395,7 +442,8 @@ moe_gate_up_mma_kernel(const bf16* __restrict__ x, int W, const bf16* __restrict
                 const int r = mt * 16 + g + (j >> 1) * 8, c = (warp * MMA_NW + t) * 8 + 2 * tg + (j & 1);
                 if (r < rows && c < n_cols)
                     hidden[(size_t)(p0 + r) * ff + col0 + c] =
-                        __float2bfloat16_rn(gated(acc[0][mt][t][j], acc[1][mt][t][j], act, limit, alpha));
+                        __float2bfloat16_rn(NM == 2 ? gated(acc[0][mt][t][j], acc[NM - 1][mt][t][j], act, limit, alpha)
+                                                    : activate(acc[0][mt][t][j], act));
             }
 }
 
@@ -480,17 +528,21 @@ __global__ void gated_act_clamped_kernel(const T* __restrict__ gu, T* __restrict
 
 QNN_API int qnn_moe_route(const void* x, int x_dt, const void* w_router, int w_dt, int T, int W, int E, int top,
                           int score_fn, int renorm, const float* correction, float out_scale, int* sel_e, float* sel_w,
-                          int extra, float* extra_out, cudaStream_t st) {
+                          int extra, float* extra_out, int n_groups, int keep_groups, cudaStream_t st) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || top > MAX_TOP || W <= 0) return QNN_ERR_ARGUMENT;
     if (extra < 0 || (extra > 0 && extra_out == nullptr)) return QNN_ERR_ARGUMENT;
+    // groups: equal groups of neighbours, and enough experts in the kept groups for the choice
+    if (n_groups < 1) n_groups = keep_groups = 1;
+    if (E % n_groups || keep_groups < 1 || keep_groups > n_groups || (long long)keep_groups * (E / n_groups) < top)
+        return QNN_ERR_ARGUMENT;
     const int warps = E >= 8 ? 8 : (E >= 4 ? 4 : 2);
-    const size_t smem = (size_t)2 * E * sizeof(float);
+    const size_t smem = ((size_t)2 * E + n_groups) * sizeof(float);
     if (smem > 48 * 1024) return QNN_ERR_UNSUPPORTED;
     const dim3 grid(T), block(warps * 32);
 #define QNN_ROUTE(TX, TW)                                                                                         \
     launch_pdl(moe_route_kernel<TX, TW>, grid, block, smem, st, (const TX*)x, (const TW*)w_router, T, W, E, top,  \
-               score_fn, renorm, correction, out_scale, sel_e, sel_w, extra, extra_out)
+               score_fn, renorm, correction, out_scale, sel_e, sel_w, extra, extra_out, n_groups, keep_groups)
     if (x_dt == QNN_DT_BF16 && w_dt == QNN_DT_BF16) QNN_ROUTE(bf16, bf16);
     else if (x_dt == QNN_DT_BF16) QNN_ROUTE(bf16, float);
     else if (w_dt == QNN_DT_BF16) QNN_ROUTE(float, bf16);
@@ -517,39 +569,52 @@ QNN_API int qnn_moe_plan(const int* sel_e, int n, int E, int tile_rows, int* off
     QNN_LAUNCH_CHECK();
 }
 
+// act: the gate's activation (QNN_ACT_GELU_TANH, QNN_ACT_SILU or QNN_GATED_SWIGLU_CLAMPED); with QNN_ACT_ALONE added the
+// experts have no gate: w_gu is [E, ff, W] (up rows alone) and hidden = act(up(x)), act any QNN_ACT_* code.
 QNN_API int qnn_moe_gate_up(const void* x, int dtype, int W, const void* w_gu, int ff, const int* offsets, const int* perm,
                             const float* sel_w, const int* tiles, const int* n_tiles, int max_tiles, int tile_rows,
                             int top, int scale_input, int act, float limit, float alpha, void* hidden, cudaStream_t st) {
     if (max_tiles <= 0) return 0;
     if (W <= 0 || ff <= 0 || top <= 0) return QNN_ERR_ARGUMENT;
     if (tile_rows != 16 && tile_rows != 64) return QNN_ERR_ARGUMENT;
+    const bool alone = (act & QNN_ACT_ALONE) != 0;
+    act &= ~QNN_ACT_ALONE;
     if (mma_takes(dtype, W, x, w_gu)) {
         const dim3 mgrid(max_tiles, (ff + MMA_COLS - 1) / MMA_COLS);
         if (mgrid.y > 65535) return QNN_ERR_UNSUPPORTED;
         const size_t smem = (size_t)tile_rows * MMA_PITCH * sizeof(bf16);
-        if (tile_rows == 64) {
-            static bool set = false;
-            if (!set) {
-                cudaFuncSetAttribute(moe_gate_up_mma_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                set = true;
-            }
-            launch_pdl(moe_gate_up_mma_kernel<4>, mgrid, dim3(MMA_WARPS * 32), smem, st, (const bf16*)x, W, (const bf16*)w_gu,
-                       ff, offsets, perm, sel_w, tiles, n_tiles, top, scale_input, act, limit, alpha, (bf16*)hidden);
-        } else {
-            launch_pdl(moe_gate_up_mma_kernel<1>, mgrid, dim3(MMA_WARPS * 32), smem, st, (const bf16*)x, W, (const bf16*)w_gu,
-                       ff, offsets, perm, sel_w, tiles, n_tiles, top, scale_input, act, limit, alpha, (bf16*)hidden);
+#define QNN_GU_MMA(MT, NM)                                                                                             \
+        {                                                                                                              \
+            static bool set = false;                                                                                   \
+            if (smem > 48 * 1024 && !set) {                                                                            \
+                cudaFuncSetAttribute(moe_gate_up_mma_kernel<MT, NM>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                     (int)smem);                                                                       \
+                set = true;                                                                                            \
+            }                                                                                                          \
+            launch_pdl(moe_gate_up_mma_kernel<MT, NM>, mgrid, dim3(MMA_WARPS * 32), smem, st, (const bf16*)x, W,      \
+                       (const bf16*)w_gu, ff, offsets, perm, sel_w, tiles, n_tiles, top, scale_input, act, limit,      \
+                       alpha, (bf16*)hidden);                                                                          \
         }
+        if (tile_rows == 64) {
+            if (alone) QNN_GU_MMA(4, 1) else QNN_GU_MMA(4, 2)
+        } else {
+            if (alone) QNN_GU_MMA(1, 1) else QNN_GU_MMA(1, 2)
+        }
+#undef QNN_GU_MMA
         QNN_LAUNCH_CHECK();
     }
     if (tile_rows != TILE_ROWS) return QNN_ERR_ARGUMENT;
     const dim3 grid(max_tiles, (ff + TILE_COLS - 1) / TILE_COLS);
     if (grid.y > 65535) return QNN_ERR_UNSUPPORTED;
-    if (dtype == QNN_DT_BF16)
-        launch_pdl(moe_gate_up_kernel<bf16>, grid, dim3(TILE_COLS), 0, st, (const bf16*)x, W, (const bf16*)w_gu, ff, offsets,
-                   perm, sel_w, tiles, n_tiles, top, scale_input, act, limit, alpha, (bf16*)hidden);
-    else
-        launch_pdl(moe_gate_up_kernel<float>, grid, dim3(TILE_COLS), 0, st, (const float*)x, W, (const float*)w_gu, ff,
-                   offsets, perm, sel_w, tiles, n_tiles, top, scale_input, act, limit, alpha, (float*)hidden);
+#define QNN_GU(T, NM)                                                                                                  \
+    launch_pdl(moe_gate_up_kernel<T, NM>, grid, dim3(TILE_COLS), 0, st, (const T*)x, W, (const T*)w_gu, ff, offsets,  \
+               perm, sel_w, tiles, n_tiles, top, scale_input, act, limit, alpha, (T*)hidden)
+    if (dtype == QNN_DT_BF16) {
+        if (alone) QNN_GU(bf16, 1); else QNN_GU(bf16, 2);
+    } else {
+        if (alone) QNN_GU(float, 1); else QNN_GU(float, 2);
+    }
+#undef QNN_GU
     QNN_LAUNCH_CHECK();
 }
 

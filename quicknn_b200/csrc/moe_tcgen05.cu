@@ -20,6 +20,7 @@ using namespace qnn;
 
 #define EPI_NONE 0
 #define EPI_GATED 2
+#define EPI_ACT 5               // experts without a gate: out = act(rows w^T), bfloat16 in the gathered order
 
 namespace {
 
@@ -203,6 +204,9 @@ moe_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                             f[j] = __fdividef(g, 1.f + __expf(-g)) * __uint_as_float(u[j]);
                         }
                     }
+                } else if (EPI == EPI_ACT) {                     // scale_output carries the activation's code
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) f[j] = qnn::activate_fast(__uint_as_float(v[j]), scale_output);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]) * sw;
@@ -214,7 +218,7 @@ moe_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bars->acc_free[a])) : "memory");
                 }
                 if (r < rows) {
-                    if (EPI == EPI_GATED) {
+                    if (EPI != EPI_NONE) {
                         bf16* dst = reinterpret_cast<bf16*>(out) + (size_t)(m0 + r) * Nout + n0 + c0;
                         if (n0 + c0 + 32 <= Nout && ((Nout & 7) == 0)) {
 #pragma unroll
@@ -278,7 +282,8 @@ QNN_API int qnn_moe_gather(const void* x, int W, const int* perm, const float* s
 }
 
 // rows: the gathered rows [n_entries, K] bfloat16; w: [E * N, K] bfloat16, expert after expert.  epi 2: out =
-// bfloat16 [n_entries, N / 2] in the gathered order; epi 0: out = float32 [n_entries, N], row perm[p] <- gathered row p.
+// bfloat16 [n_entries, N / 2] in the gathered order; epi 5: out = act(product), bfloat16 [n_entries, N] in the gathered
+// order, the activation's code in `scale_output`; epi 0: out = float32 [n_entries, N], row perm[p] <- gathered row p.
 // tiles / n_row_tiles: the plan's list of (expert, first row) for tiles of 128 rows; max_row_tiles bounds it.
 QNN_API int qnn_moe_tcgen05(const void* rows, const void* w, void* out, int n_entries, int E, int N, int K, int epi,
                             const int* offsets, const int* perm, const float* sel_w, const int* tiles,
@@ -287,7 +292,7 @@ QNN_API int qnn_moe_tcgen05(const void* rows, const void* w, void* out, int n_en
     if (n_entries <= 0 || max_row_tiles <= 0) return 0;
     if (K <= 0 || (K & 7) || N <= 0 || E <= 0 || ((((uintptr_t)rows | (uintptr_t)w | (uintptr_t)out) & 15) != 0))
         return QNN_ERR_UNSUPPORTED;
-    if (epi != EPI_NONE && epi != EPI_GATED) return QNN_ERR_ARGUMENT;
+    if (epi != EPI_NONE && epi != EPI_GATED && epi != EPI_ACT) return QNN_ERR_ARGUMENT;
     if (epi == EPI_GATED && (N & 1)) return QNN_ERR_ARGUMENT;
     CUtensorMap map_a, map_b;
     int rc = make_map(&map_a, rows, n_entries, K, BM);
@@ -309,6 +314,18 @@ QNN_API int qnn_moe_tcgen05(const void* rows, const void* w, void* out, int n_en
     const size_t smem = (size_t)STAGES * STAGE_BYTES + sizeof(Barriers) + 1024;
     if (epi == EPI_GATED) {
         auto kern = moe_tcgen05_kernel<EPI_GATED>;
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+        cudaError_t e = qnn::launch_pdl(kern, grid, dim3(GEMM_THREADS), smem, st, map_a, map_b, out, N, K, offsets, perm,
+                                        sel_w, tiles, n_row_tiles, scale_output, limit, alpha, status);
+        return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+    }
+    if (epi == EPI_ACT) {
+        auto kern = moe_tcgen05_kernel<EPI_ACT>;
         static bool configured = false;
         if (!configured) {
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

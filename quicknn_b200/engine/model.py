@@ -60,7 +60,9 @@ class Model:
             self.embedding_norm = NORMS.get(spec.embedding.norm.kind)(spec.embedding.norm)
             self.embedding_norm.load({"weight": tensors[spec.embedding.norm_tensor]}, self.dtype, self.device)
         self.final_norm = NORMS.get(spec.head.norm.kind)(spec.head.norm)
-        self.final_norm.load({"weight": tensors[spec.head.norm_tensor]}, self.dtype, self.device)
+        # a norm's weight has the norm's own checkpoint name, its other parameters that name with a suffix
+        self.final_norm.load({k: tensors[spec.head.norm_tensor if k == "weight" else f"{spec.head.norm_tensor}.{k}"]
+                              for k in type(self.final_norm).param_shapes(spec.head.norm)}, self.dtype, self.device)
         self.head = self.embedding if spec.head.tied else tensors[spec.head.tensor].contiguous()
         why = ops.linear_refusal(self.head.dtype, spec.hidden_size)
         if why:
@@ -173,13 +175,24 @@ class Model:
         else:
             x, normed = ops.embed(step.tokens, self.embedding, spec.embedding.scale), None
         step.after_layers.clear()
+        # the embedded rows once more, for the schedule entries before which they join the stream again
+        x0 = ops.embed(step.tokens, self.embedding, spec.embedding.scale) if any(e.add_embedding for e in sched) else None
         for i, e in enumerate(sched):
             line = cache.line(e.cache, writes=e.writes_cache)
             if line is not None:
                 line.has_readers = e.cache in self._lines_read
+            if e.add_embedding:
+                first = self.blocks[e.layer].first_norm()
+                if hasattr(first, "add_then"):               # the add and the layer's first norm in one kernel
+                    normed = first.add_then(x, None, step.act_dtype, extra=x0)
+                else:
+                    ops.add_(x, x0)
+                    normed = None
             # the first norm of the layer that runs next is applied by this one, in the kernel
-            # that adds this layer's last sublayer to the residual stream
-            nxt = self.blocks[sched[i + 1].layer].first_norm() if i + 1 < len(sched) else None
+            # that adds this layer's last sublayer to the residual stream (not where the embedded rows come between)
+            nxt = None
+            if i + 1 < len(sched) and not sched[i + 1].add_embedding:
+                nxt = self.blocks[sched[i + 1].layer].first_norm()
             out = self.blocks[e.layer].forward(x, step, line, normed=normed, next_norm=nxt)
             x, normed = out if nxt is not None else (out, None)
         for call in step.after_layers:         # appends that waited for the readers of their cache line

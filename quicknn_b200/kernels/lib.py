@@ -70,12 +70,13 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_gate_heads": [c_vp, c_int, c_vp, c_int, c_int, c_vp, c_int, c_int, c_int, c_int, c_vp],
     "qnn_small_linear_f32": [c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_int, c_vp, c_int, c_float, c_vp],
     "qnn_gla_scan": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_float, c_vp, c_vp, c_vp, c_vp,
-                     c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp],
+                     c_vp, c_ll, c_int, c_int, c_int, c_int, c_int, c_vp],
     "qnn_gla_scan_segments": [c_vp, c_vp, c_vp, c_ll, c_int, c_vp, c_ll, c_float, c_vp, c_vp, c_vp, c_vp,
-                              c_vp, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp],
+                              c_vp, c_ll, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_vp, c_int, c_vp],
+    "qnn_bounded_gates": [c_vp, c_int, c_ll, c_int, c_int, c_int, c_int, c_int, c_vp, c_int, c_vp, c_int, c_vp, c_vp],
     "qnn_gla_norm_gate": [c_vp, c_ll, c_vp, c_int, c_float, c_vp, c_ll, c_vp, c_ll, c_int, c_int, c_int, c_int, c_vp],
     "qnn_moe_route": [c_vp, c_int, c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_vp, c_float, c_vp, c_vp, c_int,
-                      c_vp, c_vp],
+                      c_vp, c_int, c_int, c_vp],
     "qnn_moe_tile_rows": [c_int, c_int, c_int, c_int, c_int],
     "qnn_moe_max_tiles": [c_int, c_int, c_int],
     "qnn_moe_plan": [c_vp, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp],
@@ -106,6 +107,13 @@ _SIGNATURES: Dict[str, list] = {
                       c_int, c_int, c_int, c_vp],
     "qnn_sigmoid_gate": [c_vp, c_int, c_ll, c_vp, c_int, c_ll, c_int, c_int, c_vp],
     "qnn_xielu": [c_vp, c_int, c_float, c_float, c_vp, c_ll, c_vp],
+    "qnn_dyt": [c_vp, c_int, c_float, c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_int, c_vp],
+    "qnn_add_dyt": [c_vp, c_vp, c_int, c_vp, c_float, c_vp, c_int, c_vp, c_int, c_vp, c_int, c_int, c_int, c_vp],
+    "qnn_embed_dyt": [c_vp, c_vp, c_int, c_float, c_float, c_vp, c_int, c_vp, c_int, c_vp, c_vp, c_int, c_int, c_int, c_int,
+                      c_vp],
+    "qnn_sigattn_supports": [c_int, c_int, c_int, c_int],
+    "qnn_sigattn": [c_vp, c_int, c_ll, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int,
+                    c_float, c_vp, c_vp, c_vp, c_int, c_ll, c_vp, c_ll, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp],
     "qnn_head_norm_gate": [c_vp, c_ll, c_int, c_vp, c_ll, c_vp, c_int, c_int, c_float, c_vp, c_ll, c_int, c_vp, c_ll,
                            c_int, c_int, c_int, c_int, c_vp],
 }

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -1000,7 +1000,8 @@ GLA_SEGMENTS_FROM = 512      # the longest sequence of a step from which that is
 
 def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, q_scale: float,
              seq_row0: Optional[torch.Tensor], seq_len: Optional[torch.Tensor], slots: torch.Tensor,
-             state: torch.Tensor, n_seqs: int, n_heads: int, dim: int, vdim: int, longest: int = 0) -> torch.Tensor:
+             state: torch.Tensor, n_seqs: int, n_heads: int, dim: int, vdim: int, longest: int = 0,
+             key_from_decay: bool = False) -> torch.Tensor:
     """The recurrence S = diag(a) S + k v^T, o = S^T (q q_scale) over the rows of every sequence in order, from the
     state of the sequence's slot and back into it.  ``proj`` holds q and k ([*, heads*dim]) and v ([*, heads*vdim])
     from the given columns on; ``decay`` the decays a, float32 [rows, heads*dim]; returns o, float32 [rows, heads*vdim].
@@ -1008,7 +1009,8 @@ def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torc
     ``longest``: the most rows that one sequence brings (0: unknown).  From 512 rows on the sequences are cut into
     segments of 256 rows that run side by side (the recurrence is linear in the state: each segment's own state and
     decay product first, a short pass over the segments in order, then the outputs); results differ from the walk
-    in one piece by rounding only."""
+    in one piece by rounding only.  ``key_from_decay``: the keys are 1 - a, formed in float32 inside the scan (what the
+    forget gate lets go is what is written); ``k_col`` is then not read."""
     _req(proj, "proj", None, 2)
     _req(decay, "decay", torch.float32, 2)
     _req(slots, "slots", torch.int32, 1)
@@ -1030,12 +1032,13 @@ def gla_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torc
         _lib.check(_lib.load().qnn_gla_scan_segments(
             _col_ptr(proj, q_col), _col_ptr(proj, k_col), _col_ptr(proj, v_col), proj.shape[1], dt_code(proj), _p(decay),
             decay.shape[1], float(q_scale), _p(seq_row0), _p(seq_len), _p(slots), _p(state), _p(out), out.shape[1],
-            n_seqs, n_heads, dim, vdim, GLA_SEGMENT, nseg, _p(scratch), _p(seg_decay), _stream()), "gla_scan_segments", 4)
+            n_seqs, n_heads, dim, vdim, GLA_SEGMENT, nseg, _p(scratch), _p(seg_decay), int(key_from_decay), _stream()),
+            "gla_scan_segments", 4)
         return out
     _lib.check(_lib.load().qnn_gla_scan(
         _col_ptr(proj, q_col), _col_ptr(proj, k_col), _col_ptr(proj, v_col), proj.shape[1], dt_code(proj), _p(decay),
         decay.shape[1], float(q_scale), _p(seq_row0), _p(seq_len), _p(slots), _p(state),
-        _p(out), out.shape[1], n_seqs, n_heads, dim, vdim, _stream()), "gla_scan")
+        _p(out), out.shape[1], n_seqs, n_heads, dim, vdim, int(key_from_decay), _stream()), "gla_scan")
     return out
 
 
@@ -1063,12 +1066,15 @@ GATED_CLAMPED = 2            # the gated activation g' * sigmoid(alpha g') * (u'
 
 
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, score: str = "sigmoid", renormalize: bool = False,
-              correction: Optional[torch.Tensor] = None, scale: float = 1.0, extra: int = 0):
+              correction: Optional[torch.Tensor] = None, scale: float = 1.0, extra: int = 0,
+              groups: Optional[Tuple[int, int]] = None):
     """(expert ids int32 [rows*top], scores float32 [rows*top]): the ``top`` best experts of every row by
     score(x w_router^T), logits and scores in float32, ties to the lower index.  With ``correction`` (float32, one per
     expert) the experts are ranked by score + correction and weighted by the score alone.  ``scale`` multiplies the
     weights (after the renormalisation, if any).  With ``extra`` = n the matrix has n more rows behind the experts';
-    their products with the rows come back as a third result, float32 [rows, n], and take no part in the choice."""
+    their products with the rows come back as a third result, float32 [rows, n], and take no part in the choice.
+    ``groups`` = (count, keep): the experts form ``count`` equal groups of neighbours; a group's score is the sum of
+    its two largest ranking values, and only experts of the ``keep`` best groups can be chosen."""
     _req(x, "x", None, 2)
     _req(w_router, "w_router", None, 2)
     T, W = x.shape
@@ -1084,9 +1090,12 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, score: str = "s
     sel_e = torch.empty(T * top, dtype=torch.int32, device=x.device)
     sel_w = torch.empty(T * top, dtype=torch.float32, device=x.device)
     more = torch.empty((T, int(extra)), dtype=torch.float32, device=x.device) if extra else None
+    count, keep = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+    if E % count or not (1 <= keep <= count) or keep * (E // count) < top:
+        raise ValueError(f"moe_route: {count} groups of which {keep} are kept do not fit {E} experts and top {top}")
     _lib.check(_lib.load().qnn_moe_route(_p(x), dt_code(x), _p(w_router), dt_code(w_router), T, W, E, int(top),
                                          MOE_SCORES[score], int(renormalize), _p(correction), float(scale), _p(sel_e),
-                                         _p(sel_w), int(extra), _p(more), _stream()), "moe_route")
+                                         _p(sel_w), int(extra), _p(more), count, keep, _stream()), "moe_route")
     return (sel_e, sel_w, more) if extra else (sel_e, sel_w)
 
 
@@ -1096,7 +1105,7 @@ MOE_GROUPED_FROM = 64        # rows per expert (on average) from which prompts t
 def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: int, w_gate_up: torch.Tensor,
                 w_down: torch.Tensor, activation: int, limit: float, alpha: float, weight_on_input: bool,
                 shared: Optional[torch.Tensor] = None, grouped: Optional[bool] = None,
-                shared_gate: Optional[torch.Tensor] = None, identity: bool = False) -> torch.Tensor:
+                shared_gate: Optional[torch.Tensor] = None, identity: bool = False, gated: bool = True) -> torch.Tensor:
     """sum over a row's chosen experts of down_e(act(gate_e(x'), up_e(x'))) (+ ``shared``), float32 [rows, width].
     ``activation``: ``GATED_CLAMPED`` or the code of a plain gate (act(g) * u, e.g. ``ACT_CODES["silu"]``).
     ``identity``: expert ids from the number of experts on are identity experts (their output is the row itself
@@ -1104,6 +1113,8 @@ def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: 
     output is multiplied by its sigmoid.
     The score multiplies the expert's input (x' = score * x) or its output.  w_gate_up: [experts, 2*ff, width]
     (gate rows, then up rows); w_down: [experts, width, ff].  Everything stays on the device.
+    ``gated`` False: the experts are down_e(act(up_e(x'))); w_gate_up is then [experts, ff, width] (up rows alone) and
+    ``activation`` one of ``ACT_CODES``.
 
     Three kinds of tile: with many rows per expert (prompts; bfloat16, the clamped activation, widths in whole 16-byte
     pieces) the rows are gathered expert after expert and both products are grouped tcgen05 GEMMs over tiles of 128
@@ -1114,15 +1125,18 @@ def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: 
     _req(w_down, "w_down", x.dtype, 3)
     T, W = x.shape
     E, ff2, _ = w_gate_up.shape
-    ff = ff2 // 2
-    if tuple(w_gate_up.shape) != (E, 2 * ff, W) or tuple(w_down.shape) != (E, W, ff) or sel_e.numel() != T * top:
+    nm = 2 if gated else 1
+    ff = ff2 // nm
+    if tuple(w_gate_up.shape) != (E, nm * ff, W) or tuple(w_down.shape) != (E, W, ff) or sel_e.numel() != T * top:
         raise ValueError("moe_experts: shapes do not agree")
+    if not gated and activation not in ACT_CODES.values():
+        raise ValueError("moe_experts: experts without a gate take a plain activation")
     L = _lib.load()
     n = T * top
     if grouped is None:
         grouped = n >= MOE_GROUPED_FROM * E
     grouped = bool(grouped and USE_TCGEN05 and x.dtype == torch.bfloat16
-                   and activation in (GATED_CLAMPED, ACT_CODES["silu"]) and W % 8 == 0 and ff % 8 == 0)
+                   and (activation in (GATED_CLAMPED, ACT_CODES["silu"]) or not gated) and W % 8 == 0 and ff % 8 == 0)
     if activation != GATED_CLAMPED:
         limit = 0.0                                 # the grouped product's epilogue reads "no limit" as silu(g) * u
     extra = (shared_gate, (sel_e, sel_w, E, x) if identity else None)
@@ -1140,19 +1154,21 @@ def moe_experts(x: torch.Tensor, sel_e: torch.Tensor, sel_w: torch.Tensor, top: 
         status = _p(_status_word(x.device))
         _lib.check(L.qnn_moe_gather(_p(x), W, _p(perm), _p(sel_w), top, int(weight_on_input), _p(gathered), n, _stream()),
                    "moe_gather")
-        code = L.qnn_moe_tcgen05(_p(gathered), _p(w_gate_up), _p(hidden), n, E, 2 * ff, W, EPI_GATED, _p(offsets), _p(perm),
-                                 _p(sel_w), _p(tiles), _p(n_tiles), max_tiles, 0, float(limit), float(alpha), status,
-                                 _stream())
+        # without a gate the epilogue is the activation alone, its code in the place of `scale_output`
+        code = L.qnn_moe_tcgen05(_p(gathered), _p(w_gate_up), _p(hidden), n, E, nm * ff, W, EPI_GATED if gated else EPI_ACT,
+                                 _p(offsets), _p(perm), _p(sel_w), _p(tiles), _p(n_tiles), max_tiles,
+                                 0 if gated else int(activation), float(limit), float(alpha), status, _stream())
         if code == _lib.ERR_UNSUPPORTED:           # sizes the grouped product refuses: the other tiles
             return moe_experts(x, sel_e, sel_w, top, w_gate_up, w_down, activation, limit, alpha, weight_on_input, shared,
-                               grouped=False, shared_gate=shared_gate, identity=identity)
+                               grouped=False, shared_gate=shared_gate, identity=identity, gated=gated)
         _lib.check(code, "moe_tcgen05")
         _lib.check(L.qnn_moe_tcgen05(_p(hidden), _p(w_down), _p(ys), n, E, W, ff, EPI_NONE, _p(offsets), _p(perm), _p(sel_w),
                                      _p(tiles), _p(n_tiles), max_tiles, int(not weight_on_input), 0.0, 0.0, status,
                                      _stream()), "moe_tcgen05")
         return _moe_sum(L, ys, top, shared, T, W, *extra)
     _lib.check(L.qnn_moe_gate_up(_p(x), dt_code(x), W, _p(w_gate_up), ff, _p(offsets), _p(perm), _p(sel_w), _p(tiles),
-                                 _p(n_tiles), max_tiles, tile_rows, top, int(weight_on_input), int(activation), float(limit),
+                                 _p(n_tiles), max_tiles, tile_rows, top, int(weight_on_input),
+                                 int(activation) + (0 if gated else ACT_ALONE), float(limit),
                                  float(alpha), _p(hidden), _stream()), "moe_gate_up")
     _lib.check(L.qnn_moe_down(_p(hidden), dt_code(x), ff, _p(w_down), W, _p(offsets), _p(perm), _p(sel_w), _p(tiles),
                               _p(n_tiles), max_tiles, tile_rows, int(not weight_on_input), _p(ys), _stream()), "moe_down")
@@ -1302,7 +1318,8 @@ def head_prep(src: torch.Tensor, col0: int, n_q: int, n_k: int, n_v_cols: int, h
               q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None, norm_dim: int = 0,
               eps: float = 0.0, rot_dim: int = 0, inv_freq: Optional[torch.Tensor] = None, interleaved: bool = False,
               tok_pos: Optional[torch.Tensor] = None, tok_slot: Optional[torch.Tensor] = None, line=None,
-              append: bool = False, norm_whole: bool = False) -> torch.Tensor:
+              append: bool = False, norm_whole: bool = False, norm_last: bool = False, plain_norm: bool = False,
+              values_are_keys: bool = False) -> torch.Tensor:
     """Bias, an RMS norm per head of queries and keys, rotation and the append to a cache line, in one kernel.
 
     ``src``: rows that hold, from column ``col0`` on, ``n_q`` query heads and ``n_k`` key heads of ``head_dim`` columns
@@ -1312,12 +1329,22 @@ def head_prep(src: torch.Tensor, col0: int, n_q: int, n_k: int, n_v_cols: int, h
     (j, j + rot_dim/2) or, ``interleaved``, (2j, 2j + 1).  ``append``: keys and values go to ``line``.
     ``norm_whole``: one norm over all query heads together and one over all key heads together instead of one per
     head (the first ``norm_dim`` columns of every head count); the weights are then [n_q * norm_dim] and
-    [n_k * norm_dim]."""
+    [n_k * norm_dim].  ``norm_last``: the heads are rotated first and normed then.  ``plain_norm``: the norm has no
+    weights (``q_norm`` and ``k_norm`` stay None, ``norm_dim`` says how many columns).  ``values_are_keys``: ``src`` holds
+    queries and keys only; the ``n_v_cols`` = ``n_k * head_dim`` value columns of ``dst`` (another buffer) and the
+    line's values are the keys as they are after the bias, before norm and rotation."""
     _req(src, "src", None, 2)
     T = src.shape[0]
     width = (n_q + n_k) * head_dim + n_v_cols
-    if col0 + width > src.shape[1]:
+    if values_are_keys:
+        if dst is None or dst is src or n_v_cols != n_k * head_dim:
+            raise ValueError("head_prep: values that are the keys go to another buffer, as many columns as the keys")
+        if col0 + (n_q + n_k) * head_dim > src.shape[1]:
+            raise ValueError("head_prep: the heads do not fit the rows")
+    elif col0 + width > src.shape[1]:
         raise ValueError("head_prep: the heads do not fit the rows")
+    if plain_norm and (q_norm is not None or k_norm is not None or norm_dim <= 0):
+        raise ValueError("head_prep: a norm without weights takes none, and a number of columns")
     if dst is None:
         dst, dst_col0 = src, col0
     _req(dst, "dst", None, 2)
@@ -1325,7 +1352,7 @@ def head_prep(src: torch.Tensor, col0: int, n_q: int, n_k: int, n_v_cols: int, h
         raise ValueError("head_prep: the destination does not fit")
     if bias is not None:
         _req(bias, "bias", None, 1)
-        if bias.numel() != width:
+        if bias.numel() != (width - n_v_cols if values_are_keys else width):
             raise ValueError(f"head_prep: the bias has {bias.numel()} elements for {width} columns")
     wdt = 0
     for w, heads in ((q_norm, n_q), (k_norm, n_k)):
@@ -1358,7 +1385,9 @@ def head_prep(src: torch.Tensor, col0: int, n_q: int, n_k: int, n_v_cols: int, h
         _col_ptr(src, col0), dt_code(src), src.shape[1], _col_ptr(dst, dst_col0), dt_code(dst), dst.shape[1], T, n_q, n_k,
         n_v_cols, head_dim, int(norm_dim), int(rot_dim), int(interleaved), _p(bias), dt_code(bias) if bias is not None else 0,
         _p(q_norm), _p(k_norm), wdt, float(eps), _p(inv_freq) if rot_dim else None, _p(tok_pos), _p(tok_slot), _p(k_pool),
-        _p(v_pool), _p(table), max_pages, page_size, ring, _p(slot_len), int(append), int(norm_whole), _stream()), "head_prep")
+        _p(v_pool), _p(table), max_pages, page_size, ring, _p(slot_len), int(append),
+        int(norm_whole) | (2 if norm_last else 0) | (4 if plain_norm else 0) | (8 if values_are_keys else 0), _stream()),
+        "head_prep")
     return dst
 
 
@@ -1450,18 +1479,25 @@ def mlstm_gates(pre: torch.Tensor, bias: torch.Tensor, cap: float, seq_row0: Opt
     return gates
 
 
-def head_norm_gate(o: torch.Tensor, head_stride: int, n_heads: int, vdim: int, eps: float, gate: torch.Tensor, g_col: int,
-                   gate_act: str, weight: Optional[torch.Tensor] = None, den: Optional[torch.Tensor] = None,
-                   den_col: int = 0) -> torch.Tensor:
+def head_norm_gate(o: torch.Tensor, head_stride: int, n_heads: int, vdim: int, eps: float, gate: Optional[torch.Tensor],
+                   g_col: int, gate_act: str, weight: Optional[torch.Tensor] = None, den: Optional[torch.Tensor] = None,
+                   den_col: int = 0, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """Per head of ``o`` (float32 [rows, heads * head_stride]): divided by max(|o[vdim]|, den) + 1e-6 when ``den``
     (float32 rows, one number per head from column ``den_col`` on) is given; an RMS norm over the first ``vdim``
     columns; times ``weight`` ([vdim]: shared by the heads, [heads * vdim]: per column of the row, None: none); times
-    silu or sigmoid of the gate columns of ``gate`` (from ``g_col`` on).  Returns [rows, heads * vdim] of gate's type."""
+    silu or sigmoid of the gate columns of ``gate`` (from ``g_col`` on).  Returns [rows, heads * vdim] of gate's type.
+    ``gate_act`` "none" (``gate`` None): no gate, the result has ``out_dtype``."""
     _req(o, "o", torch.float32, 2)
-    _req(gate, "gate", None, 2)
     T = o.shape[0]
-    if o.shape[1] != n_heads * head_stride or gate.shape[0] != T or g_col + n_heads * vdim > gate.shape[1]:
-        raise ValueError("head_norm_gate: shapes do not agree")
+    if gate_act == "none":
+        if gate is not None or out_dtype is None:
+            raise ValueError("head_norm_gate: without a gate, no gate rows and an element type for the result")
+        if o.shape[1] != n_heads * head_stride:
+            raise ValueError("head_norm_gate: shapes do not agree")
+    else:
+        _req(gate, "gate", None, 2)
+        if o.shape[1] != n_heads * head_stride or gate.shape[0] != T or g_col + n_heads * vdim > gate.shape[1]:
+            raise ValueError("head_norm_gate: shapes do not agree")
     mode = 0
     if weight is not None:
         _req(weight, "weight", None, 1)
@@ -1470,11 +1506,12 @@ def head_norm_gate(o: torch.Tensor, head_stride: int, n_heads: int, vdim: int, e
             raise ValueError("head_norm_gate: the weight has vdim or heads * vdim elements")
     if den is not None:
         _req(den, "den", torch.float32, 2)
-    out = torch.empty((T, n_heads * vdim), dtype=gate.dtype, device=o.device)
+    out = torch.empty((T, n_heads * vdim), dtype=gate.dtype if gate is not None else out_dtype, device=o.device)
     _lib.check(_lib.load().qnn_head_norm_gate(
         _p(o), o.shape[1], head_stride, _col_ptr(den, den_col) if den is not None else None,
         den.shape[1] if den is not None else 0, _p(weight), dt_code(weight) if weight is not None else 0, mode, float(eps),
-        _col_ptr(gate, g_col), gate.shape[1], {"silu": 0, "sigmoid": 1}[gate_act], _p(out), out.shape[1], dt_code(gate), T,
+        _col_ptr(gate, g_col) if gate is not None else None, gate.shape[1] if gate is not None else 0,
+        {"silu": 0, "sigmoid": 1, "none": 2}[gate_act], _p(out), out.shape[1], dt_code(out), T,
         n_heads, vdim, _stream()), "head_norm_gate")
     return out
 
@@ -1564,3 +1601,144 @@ def xielu_(x: torch.Tensor, ap: float, an: float) -> torch.Tensor:
     _req(x, "x")
     _lib.check(_lib.load().qnn_xielu(_p(x), dt_code(x), float(ap), float(an), _p(x), x.numel(), _stream()), "xielu")
     return x
+
+
+# ---- dynamic tanh ------------------------------------------------------------------------------------------------------
+
+def dyt(x: torch.Tensor, alpha: float, weight: torch.Tensor, bias: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """tanh(alpha x) * weight + bias over every row, float32 math."""
+    _req(x, "x", None, 2)
+    _req(weight, "weight", None, 1)
+    _req(bias, "bias", None, 1)
+    T, H = x.shape
+    if weight.numel() != H or bias.numel() != H:
+        raise ValueError("dyt: a weight and a bias per column")
+    out = torch.empty((T, H), dtype=out_dtype, device=x.device)
+    _lib.check(_lib.load().qnn_dyt(_p(x), dt_code(x), float(alpha), _p(weight), dt_code(weight), _p(bias), dt_code(bias),
+                                   _p(out), dt_code(out), T, H, _stream()), "dyt")
+    return out
+
+
+def add_dyt(resid: torch.Tensor, a: Optional[torch.Tensor], c: Optional[torch.Tensor] = None, alpha: float = 0.0,
+            weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+            out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """resid += a (+ c) in place (float32 stream; ``a`` a sublayer's output, ``c`` float32 rows; either may be None), and,
+    with ``weight``, tanh(alpha resid) * weight + bias of the new stream in the same kernel."""
+    _req(resid, "resid", torch.float32, 2)
+    T, H = resid.shape
+    for t, what in ((a, "a"), (c, "c")):
+        if t is not None:
+            _req(t, what, torch.float32 if what == "c" else None, 2)
+            if tuple(t.shape) != (T, H):
+                raise ValueError("add_dyt: shapes do not agree")
+    out = None
+    if weight is not None:
+        _req(weight, "weight", None, 1)
+        _req(bias, "bias", None, 1)
+        if weight.numel() != H or bias.numel() != H or out_dtype is None:
+            raise ValueError("add_dyt: a weight and a bias per column, and an element type for the result")
+        out = torch.empty((T, H), dtype=out_dtype, device=resid.device)
+    _lib.check(_lib.load().qnn_add_dyt(_p(resid), _p(a), dt_code(a) if a is not None else 0, _p(c), float(alpha), _p(weight),
+                                       dt_code(weight) if weight is not None else 0, _p(bias),
+                                       dt_code(bias) if bias is not None else 0, _p(out),
+                                       dt_code(out) if out is not None else 0, T, H, _stream()), "add_dyt")
+    return out
+
+
+def embed_dyt(tokens: torch.Tensor, table: torch.Tensor, scale: float, alpha: float, weight: torch.Tensor,
+              bias: torch.Tensor, out_dtype: torch.dtype):
+    """(x, dyt(x)) with x = table[tokens] * scale (float32), in one kernel."""
+    _req(tokens, "tokens", torch.int32, 1)
+    _req(table, "table", None, 2)
+    T, (V, H) = tokens.numel(), table.shape
+    x = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    out = torch.empty((T, H), dtype=out_dtype, device=table.device)
+    _lib.check(_lib.load().qnn_embed_dyt(_p(tokens), _p(table), dt_code(table), float(scale), float(alpha), _p(weight),
+                                         dt_code(weight), _p(bias), dt_code(bias), _p(x), _p(out), dt_code(out), T, H, V,
+                                         _stream()), "embed_dyt")
+    return x, out
+
+
+# ---- gates of a matrix memory whose forget gate also writes ---------------------------------------------------------------
+
+def bounded_gates(rows: torch.Tensor, q_col: int, n_q: int, f_col: int, n_f: int, bias: Optional[torch.Tensor],
+                  lower: Optional[torch.Tensor]) -> torch.Tensor:
+    """In place: silu over the ``n_q`` query columns of ``rows`` (from ``q_col``).  Returns the forget gates
+    f = lower + (1 - lower) * sigmoid(z + bias), float32 [rows, n_f], of the pre-activations z in the ``n_f`` columns from
+    ``f_col`` (``bias`` and ``lower`` one per channel; None: 0)."""
+    _req(rows, "rows", None, 2)
+    T = rows.shape[0]
+    if q_col + n_q > rows.shape[1] or f_col + n_f > rows.shape[1]:
+        raise ValueError("bounded_gates: the columns do not fit the rows")
+    for t in (bias, lower):
+        if t is not None:
+            _req(t, "bias / lower", None, 1)
+            if t.numel() != n_f:
+                raise ValueError("bounded_gates: one bias and one lower bound per channel")
+    f = torch.empty((T, n_f), dtype=torch.float32, device=rows.device)
+    _lib.check(_lib.load().qnn_bounded_gates(_p(rows), dt_code(rows), rows.shape[1], T, q_col, n_q, f_col, n_f, _p(bias),
+                                             dt_code(bias) if bias is not None else 0, _p(lower),
+                                             dt_code(lower) if lower is not None else 0, _p(f), _stream()), "bounded_gates")
+    return f
+
+
+# ---- attention with sigmoid weights and mixed heads ----------------------------------------------------------------------
+
+MASKS = {"causal": 0, "window": 1, "chunk": 2}
+
+
+def sigmoid_attention_refusal(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int) -> Optional[str]:
+    """Why the sigmoid attention kernel does not take these sizes, or None."""
+    if n_kv < 1 or n_heads % n_kv:
+        return f"{n_kv} kv heads do not divide {n_heads} heads"
+    if not _lib.load().qnn_sigattn_supports(1 if dtype == torch.bfloat16 else 0, n_heads, n_kv, head_dim):
+        return (f"{n_heads} heads of {head_dim} columns with {n_kv} kv heads are beyond the sigmoid attention kernel "
+                f"(heads x head size up to 4096, a tile of keys within shared memory)")
+    return None
+
+
+def sigmoid_attention(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_pos: torch.Tensor,
+                      tok_row0: Optional[torch.Tensor], tok_slot: Optional[torch.Tensor], line, own_rows: bool,
+                      mask: str, mask_size: int, scale: float, pb: Optional[torch.Tensor], talk: Optional[torch.Tensor],
+                      gate: Optional[torch.Tensor], gate_col: int = 0, splits: int = 1) -> torch.Tensor:
+    """o_h(i) = sigmoid(gate[i, h]) * sum_j (sum_g talk[h, g] sigmoid(scale q_g(i) . k(j) + pb[g])) v(j) over the keys j
+    that position i sees (``mask``: "causal", "window" or "chunk" of ``mask_size``).  ``qkv``: the step's packed q | k | v
+    rows.  ``own_rows``: keys at or after the position of a sequence's first row of this step are read from ``qkv``,
+    earlier ones from the cache ``line``; False: every key from the line (a decode step after its append).  ``gate``:
+    rows whose columns ``gate_col`` .. hold one logit per head (None: no gate).  ``splits``: key ranges per token that
+    run as separate blocks and are summed in order.  Returns [rows, heads * head_dim] of qkv's type."""
+    _req(qkv, "qkv", None, 2)
+    _req(tok_pos, "tok_pos", torch.int32, 1)
+    T = qkv.shape[0]
+    H, G, D = n_heads, n_kv, head_dim
+    if qkv.shape[1] < (H + 2 * G) * D or tok_pos.numel() < T:
+        raise ValueError("sigmoid_attention: the rows are narrower than q | k | v, or positions are missing")
+    if pb is not None:
+        _req(pb, "pb", torch.float32, 1)
+    if talk is not None:
+        _req(talk, "talk", torch.float32, 2)
+    if (pb is not None and pb.numel() != H) or (talk is not None and tuple(talk.shape) != (H, H)):
+        raise ValueError("sigmoid_attention: a bias per head and a mixing matrix [heads, heads]")
+    k_pool = v_pool = table = None
+    max_pages = page_size = ring = 0
+    if line is not None:
+        k_pool, v_pool, table = line.k, line.v, line.page_table
+        if k_pool.dtype != qkv.dtype or tuple(k_pool.shape[1:]) != (G, line.page_size, D):
+            raise ValueError("sigmoid_attention: the cache line does not fit the keys")
+        max_pages, page_size, ring = table.shape[1], line.page_size, line.ring
+    elif not own_rows:
+        raise ValueError("sigmoid_attention: keys come from the step's rows or from a cache line")
+    if gate is not None:
+        _req(gate, "gate", None, 2)
+        if gate.shape[0] != T or gate_col + H > gate.shape[1]:
+            raise ValueError("sigmoid_attention: a gate logit per row and head")
+    out = torch.empty((T, H * D), dtype=qkv.dtype, device=qkv.device)
+    splits = max(1, int(splits))
+    partial = torch.empty((splits, T, H * D), dtype=torch.float32, device=qkv.device) if splits > 1 else None
+    _lib.check(_lib.load().qnn_sigattn(
+        _p(qkv), dt_code(qkv), qkv.shape[1], _p(k_pool), _p(v_pool), _p(table), max_pages, page_size, ring, _p(tok_pos),
+        _p(tok_row0), _p(tok_slot), int(own_rows), MASKS[mask], int(mask_size or 0), float(scale), _p(pb), _p(talk),
+        _col_ptr(gate, gate_col) if gate is not None else None, dt_code(gate) if gate is not None else 0,
+        gate.shape[1] if gate is not None else 0, _p(out), out.shape[1], _p(partial), splits, T, H, G, D, _stream()),
+        "sigmoid_attention", 2 if splits > 1 else 1)
+    return out

@@ -4,7 +4,8 @@
 and after each sublayer, the post-norm applied to the sublayer's output before it
 is added:  x += post(mixer(pre(x)));  x += post(ff(pre(x))).
 ``prenorm``: x += m mixer(pre(x));  x += m ff(pre(x)), with a constant m (``residual_mult``, 1 unless given) and a
-feed-forward that a layer may lack.
+feed-forward that a layer may lack.  The add and the norm that follows are one kernel for an RMSNorm and for every norm
+that offers ``add_then`` (the dynamic tanh).
 
 ``postnorm``: x += norm(mixer(x));  x += norm(ff(x)): the sublayers read the stream itself and only what they give
 is normed (a layer norm here; any norm unfused).  A mixer's ``out_bias`` and the mean of a ``parallel`` mixer's
@@ -133,6 +134,8 @@ class PreNormBlock(_LayerParts):
         """resid += mult * y, and then(resid) in the same kernel when ``then`` is an RMSNorm."""
         if isinstance(then, RMSNorm):
             return ops.add_scaled_rmsnorm(resid, y, self.mult, then.weight, then.eps, then.unit_offset, act)
+        if self.mult == 1.0 and hasattr(then, "add_then"):       # a norm that has the add in its own kernel
+            return then.add_then(resid, y, act)
         if self.mult == 1.0:
             ops.add_(resid, y)
         else:

@@ -1,4 +1,5 @@
-"""Gated linear attention: a recurrent mixer whose state is a matrix per head.
+"""Gated linear attention: a recurrent mixer whose state is a matrix per head (``gla``), and its sibling whose forget
+gate also decides what is written (``hgrn2``, below).
 
     q = W_q x * dim^(-1/2),  k = W_k x  (heads x dim),   v = W_v x  (heads x vdim)
     a = sigmoid(W_a2 (W_a1 x) + b)^(1/tau)               a decay per key channel, float32
@@ -84,3 +85,69 @@ class GatedLinearAttention(Mixer):
                          longest=0 if step.mode == "decode" else step.max_q_len)
         g = ops.gla_norm_gate(o, self.norm, self.eps, p, 2 * H * d + H * vd, H, vd)
         return project(g, self.w_o)
+
+
+@MIXERS.register("hgrn2")
+class HGRN2(Mixer):
+    """A matrix memory without keys: the forget gate decays the rows of the state and its complement is written
+    (Qin et al., "HGRN2: Gated Linear RNNs with State Expansion").
+
+        q = silu(W_q x)  (heads x dim),   v = W_v x  (heads x vdim)
+        f = l + (1 - l) * sigmoid(W_f x + b)          per head and key channel, l a learned lower bound; float32
+        S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T,   o_t = S_t^T q_t
+        y = W_o concat_h( o_h / rms(o_h) * w_norm )   w_norm: [vdim], shared by the heads
+
+    q, the gate's pre-activations and v are one stacked product; one kernel applies the silu to q and forms f in
+    float32; the scan is the ``gla`` scan with the key read as 1 - f (float32, inside the kernel).  State as ``gla``."""
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.n_heads = int(p["n_heads"])
+        self.dim = int(p["dim"])
+        self.vdim = int(p["vdim"])
+        self.eps = float(p["eps"])
+        if self.dim > 256:
+            raise ValueError(f"hgrn2: at most 256 key channels per head (got {self.dim})")
+        self.w_in: Optional[torch.Tensor] = None         # q | f | v rows
+        self.f_bias: Optional[torch.Tensor] = None
+        self.lower: Optional[torch.Tensor] = None
+        self.norm: Optional[torch.Tensor] = None
+        self.w_o: Optional[torch.Tensor] = None
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        p = spec.params
+        W, H, d, vd = int(p["hidden_size"]), int(p["n_heads"]), int(p["dim"]), int(p["vdim"])
+        M, B = cls.PARAM_ROLE_MATRIX, cls.PARAM_ROLE_NORM
+        return {"q": ((H * d, W), M), "f": ((H * d, W), M), "f_bias": ((H * d,), B), "lower": ((H * d,), B),
+                "v": ((H * vd, W), M), "norm": ((vd,), cls.PARAM_ROLE_SCALE), "o": ((W, H * vd), M)}
+
+    def load(self, tensors, compute_dtype, device) -> None:
+        self.w_in = stack_rows([tensors["q"], tensors["f"], tensors["v"]])
+        self.f_bias = tensors["f_bias"].contiguous()
+        self.lower = tensors["lower"].contiguous()
+        self.norm = tensors["norm"].contiguous()
+        self.w_o = tensors["o"].contiguous()
+
+    def weight_bytes(self) -> int:
+        ws = (self.w_in, self.f_bias, self.lower, self.norm, self.w_o)
+        return sum(w.numel() * w.element_size() for w in ws)
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return StateNeed((self.n_heads, self.dim, self.vdim), "float32")
+
+    def forward(self, x: torch.Tensor, step, line) -> torch.Tensor:
+        H, d, vd = self.n_heads, self.dim, self.vdim
+        p = project(x, self.w_in)                                         # q | f's pre-activations | v
+        f = ops.bounded_gates(p, 0, H * d, H * d, H * d, self.f_bias, self.lower)       # silu(q) in place; f, float32
+        decode = step.mode == "decode"
+        o = ops.gla_scan(p, 0, 0, 2 * H * d, f, 1.0, None if decode else step.seq_row0,
+                         None if decode else step.seq_len, step.slots, line.state, step.n_seqs, H, d, vd,
+                         longest=0 if decode else step.max_q_len, key_from_decay=True)
+        n = ops.head_norm_gate(o, vd, H, vd, self.eps, None, 0, "none", weight=self.norm, out_dtype=p.dtype)
+        return project(n, self.w_o)

@@ -17,6 +17,13 @@ m, with a normaliser vector n beside S (Beck et al., "xLSTM: Extended Long Short
     o = S_t^T q / (max(|n_t . q|, e^(-m_t)) + 1e-6)
     y = W_o ( o / rms(o) per head * w_norm * sigmoid(W_g x) )
 
+``lightning``: a fixed decay per head on queries, keys and values that pass silu; no rotation and no other scale;
+the read-out of all heads together is RMS-normed with a weight per column and multiplied by a sigmoid gate.
+
+    q = silu(W_q x),  k = silu(W_k x),  v = silu(W_v x)
+    S_t = decay_h S_{t-1} + k_t v_t^T,   o_t = S_t^T q_t
+    y = W_o ( o / rms(o over all heads) * w_norm * sigmoid(W_g x) )
+
 The state lives in the cache's fixed-size state region, float32, zeroed when the slot is handed out: for ``mlstm`` a
 slot keeps [heads, dim, vdim + 1] (the last column is n: the normaliser is the state column of a value that is 1 in
 every row) and then m per head.  One scan walks every sequence's rows in order from the slot's state and back, so
@@ -106,6 +113,51 @@ class Retention(_MatrixMemory):
                             step.slots, line.state, step.n_seqs, H, d, vd, longest=longest)
         g = ops.head_norm_gate(o, vd, H, vd, self.eps, p, 2 * H * d + H * vd, "silu")
         return project(g, self.w_o)
+
+
+@MIXERS.register("lightning")
+class LightningAttention(_MatrixMemory):
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.decay = tuple(float(d) for d in spec.params["decay"])
+        if len(self.decay) != self.n_heads:
+            raise ValueError(f"lightning: {len(self.decay)} decays for {self.n_heads} heads")
+        self.decay_dev: Optional[torch.Tensor] = None
+        self.w_gate: Optional[torch.Tensor] = None
+        self.norm: Optional[torch.Tensor] = None
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        p = spec.params
+        W, H, d, vd = int(p["hidden_size"]), int(p["n_heads"]), int(p["dim"]), int(p["vdim"])
+        M = cls.PARAM_ROLE_MATRIX
+        return {"q": ((H * d, W), M), "k": ((H * d, W), M), "v": ((H * vd, W), M), "gate": ((H * vd, W), M),
+                "o": ((W, H * vd), M), "norm": ((H * vd,), cls.PARAM_ROLE_SCALE)}
+
+    def load(self, tensors, compute_dtype, device) -> None:
+        # q | k | v are one product whose epilogue is the silu; the gate's logits are a product of their own
+        self.w_in = stack_rows([tensors["q"], tensors["k"], tensors["v"]])
+        self.w_gate = tensors["gate"].contiguous()
+        self.w_o = tensors["o"].contiguous()
+        self.norm = tensors["norm"].contiguous()
+        self.decay_dev = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(device)
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_gate, self.w_o, self.norm))
+
+    def state_need(self) -> Optional[StateNeed]:
+        return StateNeed((self.n_heads * self.dim * self.vdim,), "float32")
+
+    def forward(self, x: torch.Tensor, step, line) -> torch.Tensor:
+        H, d, vd = self.n_heads, self.dim, self.vdim
+        p = project(x, self.w_in, epilogue=ops.EPI_ACT, activation="silu")          # silu(q | k | v)
+        g = project(x, self.w_gate)
+        row0, lens, longest = self._rows(step)
+        o = ops.memory_scan(p, 0, H * d, 2 * H * d, self.decay_dev, 0, None, 0, 1.0, False, row0, lens, step.slots,
+                            line.state, step.n_seqs, H, d, vd, longest=longest)
+        # one norm over all heads together: a single "head" as wide as the row, a weight per column
+        n = ops.head_norm_gate(o, H * vd, 1, H * vd, self.eps, g, 0, "sigmoid", weight=self.norm)
+        return project(n, self.w_o)
 
 
 @MIXERS.register("mlstm")

@@ -12,7 +12,10 @@ silu(gate) * up instead of the clamped one; no ``limit``); ``correction`` (a lea
 added to the scores for the choice only; the weights are the scores without it); ``route_scale`` (multiplies the
 weights); ``identity`` = n (the router has n more outputs than there are experts; those stand for identity
 experts: such an entry contributes weight * x and owns no parameters); ``shared_gate`` (the shared
-expert's output is multiplied by sigmoid(w . x), one number per token).  Everything from the router to the sum stays on the
+expert's output is multiplied by sigmoid(w . x), one number per token); ``gated`` False (experts without a gate:
+down(act(up(x))) with ``activation`` one of ``ops.ACT_CODES``, e.g. "relu2"; each expert then owns ``up_proj`` and
+``down_proj`` only); ``groups`` = (count, keep) (the experts form ``count`` equal groups of neighbours, a group's score is
+the sum of its two largest ranking values, and only experts of the ``keep`` best groups can be chosen).  Everything from the router to the sum stays on the
 device (no count is read back), so a decode step with routed layers is captured in a CUDA graph like any other.
 """
 from __future__ import annotations
@@ -66,8 +69,20 @@ class RoutedExperts(FeedForward):
         self.top = int(p["top"])
         self.inter = int(p["intermediate_size"])
         self.activation = str(p.get("activation", "clamped"))
-        if self.activation not in ("clamped", "silu"):
+        self.gated = bool(p.get("gated", True))
+        if self.gated and self.activation not in ("clamped", "silu"):
             raise ValueError(f"routed experts: activation {self.activation!r} is neither 'clamped' nor 'silu'")
+        if not self.gated and self.activation not in ops.ACT_CODES:
+            raise ValueError(f"routed experts without a gate: activation {self.activation!r} is not one of {sorted(ops.ACT_CODES)}")
+        groups = p.get("groups")
+        self.groups = None if groups is None else (int(groups[0]), int(groups[1]))
+        if self.groups is not None:
+            count, keep = self.groups
+            if count < 1 or int(p["experts"]) % count or not (1 <= keep <= count) or keep * (int(p["experts"]) // count) < int(p["top"]):
+                raise ValueError(f"routed experts: {count} groups of which {keep} are kept do not fit "
+                                 f"{p['experts']} experts and top {p['top']}")
+            if int(p.get("identity", 0)):
+                raise ValueError("routed experts: groups of experts and identity experts do not go together")
         self.limit = float(p["limit"]) if self.activation == "clamped" else 0.0
         self.alpha = float(p.get("alpha", 1.702))
         self.identity = int(p.get("identity", 0))
@@ -104,7 +119,8 @@ class RoutedExperts(FeedForward):
         if p.get("shared_gate", False):
             out["shared_gate"] = ((1, H), M)
         for e in range(E):
-            out[f"experts.{e}.gate_proj"] = ((I, H), M)
+            if p.get("gated", True):
+                out[f"experts.{e}.gate_proj"] = ((I, H), M)
             out[f"experts.{e}.up_proj"] = ((I, H), M)
             out[f"experts.{e}.down_proj"] = ((H, I), M)
         shared: Optional[PartSpec] = p.get("shared")
@@ -116,8 +132,11 @@ class RoutedExperts(FeedForward):
     def load(self, tensors, compute_dtype, device) -> None:
         E = self.n_experts
         self.w_router = tensors["router"].contiguous()
-        self.w_gate_up = torch.stack([stack_rows([tensors[f"experts.{e}.gate_proj"], tensors[f"experts.{e}.up_proj"]])
-                                      for e in range(E)]).contiguous()
+        if self.gated:
+            self.w_gate_up = torch.stack([stack_rows([tensors[f"experts.{e}.gate_proj"], tensors[f"experts.{e}.up_proj"]])
+                                          for e in range(E)]).contiguous()
+        else:                                               # up rows alone: [experts, ff, width]
+            self.w_gate_up = torch.stack([tensors[f"experts.{e}.up_proj"] for e in range(E)]).contiguous()
         self.w_down = torch.stack([tensors[f"experts.{e}.down_proj"] for e in range(E)]).contiguous()
         if self.w_gate_up.dtype != self.w_down.dtype:
             wide = torch.float32
@@ -143,13 +162,14 @@ class RoutedExperts(FeedForward):
     def forward(self, x: torch.Tensor, step) -> torch.Tensor:
         if self.w_router_and_gate is not None:
             sel_e, sel_w, gate = ops.moe_route(x, self.w_router_and_gate, self.top, self.score, self.renormalize,
-                                               self.correction, self.route_scale, extra=1)
+                                               self.correction, self.route_scale, extra=1, groups=self.groups)
         else:
             sel_e, sel_w = ops.moe_route(x, self.w_router, self.top, self.score, self.renormalize, self.correction,
-                                         self.route_scale)
+                                         self.route_scale, groups=self.groups)
             gate = ops.small_linear_f32(x, self.w_shared_gate) if self.has_shared_gate else None
         shared = self.shared.forward(x, step) if self.shared is not None else None
         xe = x if x.dtype == self.w_gate_up.dtype else ops.cast(x, self.w_gate_up.dtype)
-        act = ops.GATED_CLAMPED if self.activation == "clamped" else ops.ACT_CODES["silu"]
+        act = ops.GATED_CLAMPED if self.activation == "clamped" else ops.ACT_CODES[self.activation]
         return ops.moe_experts(xe, sel_e, sel_w, self.top, self.w_gate_up, self.w_down, act, self.limit,
-                               self.alpha, self.weight_on_input, shared, shared_gate=gate, identity=self.identity > 0)
+                               self.alpha, self.weight_on_input, shared, shared_gate=gate, identity=self.identity > 0,
+                               gated=self.gated)

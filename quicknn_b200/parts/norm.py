@@ -7,6 +7,9 @@ reference's files hold 1 + w already (src/models/QuickNN.Models.Gemma2.pas:58), 
 checkpoints read here hold w.
 ``group_rmsnorm``: the row is cut into ``groups`` equal consecutive pieces, each is divided by its own
 sqrt(mean(piece^2) + eps), and the whole is multiplied by w (one group: an RMS norm with a plain weight).
+``dynamic_tanh``: y = tanh(alpha x) * w + b with one learned number alpha, a weight and a bias per column; no mean and
+no variance are formed (Zhu et al., "Transformers without Normalization").  Parameters ``weight``, ``alpha`` (a
+scalar) and ``b``.
 """
 from __future__ import annotations
 
@@ -121,3 +124,39 @@ class NoNorm(Norm):
 
     def __call__(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         return ops.cast(x, out_dtype)
+
+
+@NORMS.register("dynamic_tanh")
+class DynamicTanh(Norm):
+    """tanh(alpha x) * w + b.  alpha is read once, when the model is built, and travels as a kernel argument."""
+
+    def __init__(self, spec: PartSpec):
+        super().__init__(spec)
+        self.size = int(spec.params["size"])
+        self.alpha = 1.0
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        n = int(spec.params["size"])
+        return {"weight": ((n,), cls.PARAM_ROLE_SCALE), "alpha": ((), cls.PARAM_ROLE_SCALE), "b": ((n,), cls.PARAM_ROLE_NORM)}
+
+    def load(self, tensors, compute_dtype, device) -> None:
+        self.weight = tensors["weight"].contiguous()
+        self.bias = tensors["b"].contiguous()
+        self.alpha = float(tensors["alpha"].detach().to("cpu", torch.float32).reshape(()).item())
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.weight, self.bias))
+
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        return ops.dyt(x, self.alpha, self.weight, self.bias, out_dtype)
+
+    def of_embedding(self, tokens: torch.Tensor, table: torch.Tensor, scale: float, out_dtype: torch.dtype):
+        """(embedded rows, self(embedded rows)) in one kernel: the first norm of a model's first layer."""
+        return ops.embed_dyt(tokens, table, scale, self.alpha, self.weight, self.bias, out_dtype)
+
+    def add_then(self, resid: torch.Tensor, y, out_dtype: torch.dtype, extra=None) -> torch.Tensor:
+        """resid += y (+ extra, float32 rows), then self(resid), in one kernel."""
+        return ops.add_dyt(resid, y, extra, self.alpha, self.weight, self.bias, out_dtype)

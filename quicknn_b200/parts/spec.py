@@ -40,11 +40,15 @@ class LayerSpec:
 class ScheduleEntry:
     """One executed layer.  ``layer`` indexes ``ModelSpec.layers`` (weights);
     ``cache`` names the cache line that this execution reads; ``writes_cache``
-    is False when it only reads a line another entry wrote."""
+    is False when it only reads a line another entry wrote.  ``add_embedding``:
+    before this execution the embedded rows (the stream as it was before the first
+    layer) are added to the stream: a stack of layers that runs several times over
+    starts every pass but the first like this."""
 
     layer: int
     cache: int
     writes_cache: bool = True
+    add_embedding: bool = False
 
 
 @dataclasses.dataclass(frozen=True)

@@ -117,7 +117,14 @@ def chunk_visible(n: int, size: int, first_position: int = 0) -> np.ndarray:
     return (p[None, :] <= p[:, None]) & ((p[None, :] // size) == (p[:, None] // size))
 
 
-def sigmoid_attention(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, m: dict, eps: float) -> np.ndarray:
+def window_visible(n: int, size: int) -> np.ndarray:
+    """[n, n] booleans: row i sees the last ``size`` positions up to itself (a mask the design does not use; the
+    library's attention part offers it beside the chunks)."""
+    p = np.arange(n)
+    return (p[None, :] <= p[:, None]) & (p[:, None] - p[None, :] < size)
+
+
+def sigmoid_attention(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, m: dict, eps: float, see=None) -> np.ndarray:
     n = h.shape[0]
     H, G, D = int(m["heads"]), int(m["kv_heads"]), int(m["dim"])
     q = (h @ w[pre + "q"].T + w[pre + "q.b"]).reshape(n, H, D)
@@ -125,7 +132,8 @@ def sigmoid_attention(h: np.ndarray, w: Dict[str, np.ndarray], pre: str, m: dict
     v = k                                                    # the values are the keys as projected
     q = rms_unit(rotate(q, m["rot"]), eps)
     kk = rms_unit(rotate(k, m["rot"]), eps)
-    see = chunk_visible(n, int(m["mask"]["size"]))
+    if see is None:
+        see = chunk_visible(n, int(m["mask"]["size"]) if m.get("mask") else n)   # no mask: one chunk holds everything
     per = H // G
     weights = np.zeros((H, n, n), dtype=F)
     for g in range(H):
@@ -271,3 +279,24 @@ def load_folder(path: str):
     with open(os.path.join(path, "config.json"), "r", encoding="utf-8") as fh:
         cfg = json.load(fh)
     return cfg, read_safetensors(os.path.join(path, "model.safetensors"))
+
+
+class PlainGunirax:
+    """A model folder read once; whole sequences through ``forward``."""
+
+    def __init__(self, folder: str):
+        self.cfg, self.w = load_folder(folder)
+
+    def logits(self, tokens) -> np.ndarray:
+        return forward(self.cfg, self.w, tokens)
+
+    def layers(self, tokens) -> np.ndarray:
+        return forward(self.cfg, self.w, tokens, return_layers=True)[1]
+
+    def greedy(self, prompt, n: int) -> List[int]:
+        seq, out = list(prompt), []
+        for _ in range(n):
+            t = int(np.argmax(self.logits(seq)[-1]))
+            out.append(t)
+            seq.append(t)
+        return out

@@ -266,7 +266,9 @@ def design_sizes(name, design="fuposun"):
     vocabulary, window and dense feed-forward width.  ``2b``: the 2B layer sizes; ``1b``: about half of them.
     Fuposun's layers come in the pattern latent attention + dense, latent attention + experts, linear attention +
     dense, latent attention + experts; Tumudra's: windowed attention beside a matrix memory, attention, retention,
-    attention on the keys and values of the attention layer before it (all with the dense feed-forward)."""
+    attention on the keys and values of the attention layer before it (all with the dense feed-forward); Gunirax's:
+    six layers of which the second and third run twice (chunked sigmoid attention beside a lightning memory, and HGRN2,
+    with dense and routed feed-forwards in turn)."""
     W, ff, heads, hd, kvh, layers, vocab, window = {
         "2b": (2304, 9216, 8, 256, 4, 8, 32768, 4096), "1b": (1536, 6144, 8, 128, 4, 8, 32768, 2048)}[name]
     rank, qr, d = (256, 768, 128) if name == "2b" else (128, 512, 64)
@@ -285,6 +287,21 @@ def design_sizes(name, design="fuposun"):
                  query_pre_attn_scalar=hd)
     if design == "fuposun":
         return [("fuposun", fupo), ("gemma2", gemma)]
+    if design == "gunirax":
+        # eight executed layers from six: the second and third run twice over (the loop).  Chunked sigmoid attention
+        # with the other models' heads beside a lightning memory, HGRN2 layers, dense and routed feed-forwards.
+        mh = W // (2 * d)
+        gleft = {"heads": heads, "kv_heads": kvh, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window},
+                 "rot": {"base": 1e4, "dims": hd // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+        gright = {"heads": mh, "dim": d, "vdim": 2 * d, "decay": [1.0 - 2.0 ** -(5 + h % 8) for h in range(mh)]}
+        par = ("parallel", {"left": gleft, "right": gright})
+        hg = ("hgrn2", {"heads": mh, "dim": d, "vdim": 2 * d})
+        gmoe = {"kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4},
+                "router": {"experts": 16, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+        glayers = [{"type": t, "mixer": m, "mlp": f} for (t, m), f in
+                   ((par, dense), (par, gmoe), (hg, dense), (par, gmoe), (par, dense), (hg, gmoe))]
+        guni = dict(architecture="Gunirax", vocab=vocab, width=W, embedding={"scale": 1.0}, norm={"eps": 1e-6},
+                    loop={"start": 1, "stop": 3, "times": 2}, layers=glayers)
     if design == "mubasun":
         matt = {"heads": heads, "kv_heads": kvh, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window}}
         mmoe = {"kind": "moe", "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4},
@@ -314,6 +331,8 @@ def design_sizes(name, design="fuposun"):
             mixer = ("attention", dict(att, kv_from=i - 2))
         tlayers.append({"type": mixer[0], "mixer": mixer[1], "mlp": dense})
     tumu = dict(architecture="Tumudra", vocab=vocab, width=W, embedding={"scale": 1.0}, norm={"eps": 1e-6}, layers=tlayers)
+    if design == "gunirax":
+        return [("gunirax", guni), ("tumudra", tumu), ("fuposun", fupo), ("gemma2", gemma)]
     return [("tumudra", tumu), ("fuposun", fupo), ("gemma2", gemma)]
 
 
@@ -393,7 +412,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-baseline", action="store_true", help="do not time the plain PyTorch / NumPy baselines")
-    ap.add_argument("--design", default=None, choices=["fuposun", "tumudra", "mubasun"],
+    ap.add_argument("--design", default=None, choices=["fuposun", "tumudra", "mubasun", "gunirax"],
                     help="instead of the record: this design beside the library's other models at equal size "
                          "(prefill, decode, kernels)")
     ap.add_argument("--design-sizes", default="1b,2b", help="with --design: which of 1b, 2b")

@@ -14,6 +14,7 @@
 //                       packed q | k | v rows (`own_rows`), an earlier one from the paged cache line (ring aware); with
 //                       own_rows = 0 every key comes from the cache (a decode step, after its append).
 //   qnn_sigattn_finish  sums the partial outputs of the key ranges in order and applies the gate (only with ranges)
+//   qnn_sigattn_prefill_mma   whole prompts in bfloat16 on the tensor cores (further down)
 //
 // A block per (token, key range) holds the token's queries of all heads in shared memory as float32 and walks its
 // keys in tiles: scores and sigmoids of all heads for the tile, the mix over heads, then the weighted sum of the
@@ -201,6 +202,209 @@ int sa_launch(dim3 grid, size_t smem, cudaStream_t st, const void* qkv, long lon
     QNN_LAUNCH_CHECK();
 }
 
+
+// ---- whole prompts on the tensor cores (bfloat16) -------------------------------------------------------------------
+// A block owns 16 query rows of one sequence and all heads, a warp per query head.  Per tile of KT keys: every warp
+// forms its head's scores S = Q_g K^T (mma.sync m16n8k16, Q, K and V fragments by ldmatrix from padded rows), the
+// sigmoids in float32, and leaves them in shared memory; after a barrier every warp mixes the heads' weights for its
+// own head h from there, in float32 and straight into the A operand of O_h += M_h V (the mix needs every head's weight
+// of an element, which is why one block holds all heads of its rows and why the weights pass through shared
+// memory).  Keys and values are read from the step's packed rows.  The mixed weights are rounded to bfloat16 for the
+// product with the values, as the softmax kernels round theirs; sums are float32.
+
+__device__ __forceinline__ void sa_cp_async_16(unsigned smem_dst, const void* gmem_src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_dst), "l"(gmem_src), "r"(bytes));
+}
+__device__ __forceinline__ void sa_cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 0;\n" ::);
+}
+__device__ __forceinline__ void sa_ldmatrix_x4(uint32_t (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void sa_ldmatrix_x4_trans(uint32_t (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void sa_mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t sa_pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+constexpr int SAM_ROWS = 16;          // query rows of a block
+
+template <int D, int KT>
+__global__ void __launch_bounds__(D > 128 ? 256 : 512)
+sigattn_prefill_mma_kernel(const bf16* __restrict__ qkv, long long ld, const int* __restrict__ seq_row0,
+                           const int* __restrict__ seq_len, int mask_kind, int mask_size, float scale,
+                           const float* __restrict__ pb, const float* __restrict__ talk, const void* __restrict__ gate,
+                           int g_dt, long long ldg, bf16* __restrict__ out, long long ldo, int H, int G) {
+    extern __shared__ __align__(16) unsigned char sa_smem_raw[];
+    constexpr int WP = KT + 8;                       // pitch of a row of weights, floats
+    const int HD = H * D, GD = G * D, per = H / G;
+    const int QP = HD + 8, KP = GD + 8;              // pitches in elements: rows 16 bytes apart in the banks
+    bf16* qs = reinterpret_cast<bf16*>(sa_smem_raw);                 // [16][QP]
+    bf16* ks = qs + (size_t)SAM_ROWS * QP;                           // [KT][KP]
+    bf16* vs = ks + (size_t)KT * KP;                                 // [KT][KP]
+    float* ws = reinterpret_cast<float*>(vs + (size_t)KT * KP);      // [H][16][WP]
+    float* tk = ws + (size_t)H * SAM_ROWS * WP;                      // [H][H]
+    pdl_wait();
+    const int b = blockIdx.y, len = seq_len[b];
+    const int ntiles = (len + SAM_ROWS - 1) / SAM_ROWS;
+    if ((int)blockIdx.x >= ntiles) return;
+    const int tile = ntiles - 1 - blockIdx.x;        // the longest rows first
+    const int r0 = tile * SAM_ROWS, row0 = seq_row0[b];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g_ = lane >> 2, t_ = lane & 3, nthr = blockDim.x;
+    const int h = warp;                              // this warp's query head, and the head it mixes for
+    const int c = h / per;                           // its key/value head
+    const unsigned sQ = (unsigned)__cvta_generic_to_shared(qs), sK = (unsigned)__cvta_generic_to_shared(ks);
+    const unsigned sV = (unsigned)__cvta_generic_to_shared(vs);
+    for (int i = tid; i < H * H; i += nthr) tk[i] = talk != nullptr ? talk[i] : ((i / H) == (i % H) ? 1.f : 0.f);
+    {
+        const int chunks = HD / 8;
+        for (int idx = tid; idx < SAM_ROWS * chunks; idx += nthr) {
+            const int row = idx / chunks, ch = idx - row * chunks;
+            const bool valid = r0 + row < len;
+            sa_cp_async_16(sQ + (unsigned)(row * QP + ch * 8) * 2, qkv + (size_t)(row0 + (valid ? r0 + row : 0)) * ld + ch * 8, valid);
+        }
+    }
+    const int last = min(r0 + SAM_ROWS, len) - 1;    // the last position of the tile
+    int lo = 0;                                      // the first key that any row of the tile sees
+    if (mask_kind == QNN_MASK_WINDOW) lo = max(0, r0 - mask_size + 1);
+    else if (mask_kind == QNN_MASK_CHUNK) lo = (r0 / mask_size) * mask_size;
+    const int n_tiles = (last - lo) / KT + 1;
+    const float bias = pb != nullptr ? pb[h] : 0.f;
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    for (int kt = 0; kt < n_tiles; ++kt) {
+        const int j0 = lo + kt * KT;
+        __syncthreads();                             // the tile before is read
+        {
+            const int chunks = GD / 8;
+            for (int idx = tid; idx < KT * chunks; idx += nthr) {
+                const int row = idx / chunks, ch = idx - row * chunks;
+                const bool valid = j0 + row <= last;
+                const bf16* src = qkv + (size_t)(row0 + (valid ? j0 + row : 0)) * ld + HD + ch * 8;
+                sa_cp_async_16(sK + (unsigned)(row * KP + ch * 8) * 2, src, valid);
+                sa_cp_async_16(sV + (unsigned)(row * KP + ch * 8) * 2, src + GD, valid);
+            }
+        }
+        sa_cp_async_wait_all();
+        __syncthreads();
+        // the scores of this warp's head
+        float s[KT / 8][4];
+#pragma unroll
+        for (int i = 0; i < KT / 8; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+        for (int k16 = 0; k16 < D / 16; ++k16) {
+            uint32_t a[4];
+            sa_ldmatrix_x4(a, sQ + (unsigned)((lane & 15) * QP + h * D + k16 * 16 + (lane >> 4) * 8) * 2);
+#pragma unroll
+            for (int np = 0; np < KT / 16; ++np) {
+                uint32_t bfr[4];
+                const int row = np * 16 + (lane & 7) + ((lane >> 4) << 3);
+                sa_ldmatrix_x4(bfr, sK + (unsigned)(row * KP + c * D + k16 * 16 + ((lane >> 3) & 1) * 8) * 2);
+                sa_mma_16816(s[np * 2], a, bfr[0], bfr[1]);
+                sa_mma_16816(s[np * 2 + 1], a, bfr[2], bfr[3]);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < KT / 8; ++nt)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int row = g_ + half * 8, i = r0 + row;
+                int first = 0;
+                if (mask_kind == QNN_MASK_WINDOW) first = i - mask_size + 1;
+                else if (mask_kind == QNN_MASK_CHUNK) first = (i / mask_size) * mask_size;
+                float w2[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = j0 + nt * 8 + 2 * t_ + e;
+                    const bool seen = j <= i && j >= first && i < len;
+                    w2[e] = seen ? 1.f / (1.f + __expf(-(s[nt][half * 2 + e] * scale + bias))) : 0.f;
+                }
+                *reinterpret_cast<float2*>(ws + ((size_t)h * SAM_ROWS + row) * WP + nt * 8 + 2 * t_) = make_float2(w2[0], w2[1]);
+            }
+        __syncthreads();
+        // this head's mix of all heads' weights, as the A operand; O += M V
+#pragma unroll
+        for (int kk = 0; kk < KT / 16; ++kk) {
+            float m[4][2];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) m[q][0] = m[q][1] = 0.f;
+            for (int g = 0; g < H; ++g) {
+                const float tg = tk[h * H + g];
+                const float* wg = ws + (size_t)g * SAM_ROWS * WP + kk * 16 + 2 * t_;
+                const float2 x0 = *reinterpret_cast<const float2*>(wg + (size_t)g_ * WP);
+                const float2 x1 = *reinterpret_cast<const float2*>(wg + (size_t)(g_ + 8) * WP);
+                const float2 x2 = *reinterpret_cast<const float2*>(wg + (size_t)g_ * WP + 8);
+                const float2 x3 = *reinterpret_cast<const float2*>(wg + (size_t)(g_ + 8) * WP + 8);
+                m[0][0] += tg * x0.x; m[0][1] += tg * x0.y;
+                m[1][0] += tg * x1.x; m[1][1] += tg * x1.y;
+                m[2][0] += tg * x2.x; m[2][1] += tg * x2.y;
+                m[3][0] += tg * x3.x; m[3][1] += tg * x3.y;
+            }
+            uint32_t a[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) a[q] = sa_pack_bf16(m[q][0], m[q][1]);
+#pragma unroll
+            for (int dp = 0; dp < D / 16; ++dp) {
+                uint32_t bfr[4];
+                const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+                sa_ldmatrix_x4_trans(bfr, sV + (unsigned)(row * KP + c * D + dp * 16 + (lane >> 4) * 8) * 2);
+                sa_mma_16816(o[dp * 2], a, bfr[0], bfr[1]);
+                sa_mma_16816(o[dp * 2 + 1], a, bfr[2], bfr[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int i = r0 + g_ + half * 8;
+        if (i >= len) continue;
+        const size_t t = (size_t)(row0 + i);
+        float gt = 1.f;
+        if (gate != nullptr) gt = 1.f / (1.f + expf(-load_as_f(gate, g_dt, t * ldg + h)));
+#pragma unroll
+        for (int nd = 0; nd < D / 8; ++nd)
+            *reinterpret_cast<uint32_t*>(out + t * ldo + h * D + nd * 8 + 2 * t_) =
+                sa_pack_bf16(o[nd][half * 2] * gt, o[nd][half * 2 + 1] * gt);
+    }
+}
+
+size_t sam_smem(int H, int G, int D, int KT) {
+    return ((size_t)SAM_ROWS * (H * D + 8) + 2 * (size_t)KT * (G * D + 8)) * 2 +
+           ((size_t)H * SAM_ROWS * (KT + 8) + (size_t)H * H) * sizeof(float);
+}
+
+template <int D, int KT>
+int sam_launch(dim3 grid, int threads, size_t smem, cudaStream_t st, const void* qkv, long long ld, const int* seq_row0,
+               const int* seq_len, int mask_kind, int mask_size, float scale, const float* pb, const float* talk,
+               const void* gate, int g_dt, long long ldg, void* out, long long ldo, int H, int G) {
+    static size_t allowed = 48 * 1024;
+    if (smem > allowed) {
+        const cudaError_t rc = cudaFuncSetAttribute(sigattn_prefill_mma_kernel<D, KT>,
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (rc != cudaSuccess) return (int)rc;
+        allowed = smem;
+    }
+    launch_pdl(sigattn_prefill_mma_kernel<D, KT>, grid, dim3(threads), smem, st, (const bf16*)qkv, ld, seq_row0, seq_len,
+               mask_kind, mask_size, scale, pb, talk, gate, g_dt, ldg, (bf16*)out, ldo, H, G);
+    QNN_LAUNCH_CHECK();
+}
+
 }  // namespace
 
 // Sizes that the kernel takes: heads * head size up to 4096, kv heads that divide the heads, and tiles of at least 8 keys
@@ -257,4 +461,35 @@ QNN_API int qnn_sigattn(const void* qkv, int dtype, long long ld, const void* k_
         launch_pdl(sigattn_finish_kernel<float>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (const float*)partial,
                    n_split, gate, g_dt, ldg, (float*)out, ldo, T, H * D, D);
     QNN_LAUNCH_CHECK();
+}
+
+// Whole prompts (every sequence of the step starts at position 0) in bfloat16 on the tensor cores.  qkv, pb, talk, gate
+// and out as for qnn_sigattn; seq_row0 / seq_len: first row and length of each of the B sequences; longest: the longest
+// of them.  Head sizes 32, 64, 128 (up to 16 heads) and 256 (up to 8 heads), rows in whole 16-byte pieces; anything
+// else is refused with QNN_ERR_UNSUPPORTED and the caller takes qnn_sigattn.
+QNN_API int qnn_sigattn_prefill_mma(const void* qkv, long long ld, const int* seq_row0, const int* seq_len, int B,
+                                    int longest, int mask_kind, int mask_size, float scale, const float* pb,
+                                    const float* talk, const void* gate, int g_dt, long long ldg, void* out,
+                                    long long ldo, int H, int G, int D, cudaStream_t st) {
+    if (B <= 0 || longest <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || H > (D > 128 ? 8 : 16)) return QNN_ERR_UNSUPPORTED;
+    if (D != 32 && D != 64 && D != 128 && D != 256) return QNN_ERR_UNSUPPORTED;
+    if (ld % 8 || ldo % 2 || ((uintptr_t)qkv % 16) || ((uintptr_t)out % 4) || B > 65535) return QNN_ERR_UNSUPPORTED;
+    if (mask_kind < 0 || mask_kind > 2 || (mask_kind != QNN_MASK_CAUSAL && mask_size < 1)) return QNN_ERR_ARGUMENT;
+    if (seq_row0 == nullptr || seq_len == nullptr) return QNN_ERR_ARGUMENT;
+    int KT = 32;
+    if (sam_smem(H, G, D, KT) > 220 * 1024) KT = 16;
+    const size_t smem = sam_smem(H, G, D, KT);
+    if (smem > 220 * 1024) return QNN_ERR_UNSUPPORTED;
+    const dim3 grid((longest + SAM_ROWS - 1) / SAM_ROWS, B);
+#define QNN_SAM(DV)                                                                                                   \
+    return KT == 32 ? sam_launch<DV, 32>(grid, H * 32, smem, st, qkv, ld, seq_row0, seq_len, mask_kind, mask_size, scale, \
+                                         pb, talk, gate, g_dt, ldg, out, ldo, H, G)                                   \
+                    : sam_launch<DV, 16>(grid, H * 32, smem, st, qkv, ld, seq_row0, seq_len, mask_kind, mask_size, scale, \
+                                         pb, talk, gate, g_dt, ldg, out, ldo, H, G)
+    if (D == 32) QNN_SAM(32);
+    if (D == 64) QNN_SAM(64);
+    if (D == 128) QNN_SAM(128);
+    QNN_SAM(256);
+#undef QNN_SAM
 }

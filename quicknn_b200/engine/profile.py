@@ -217,6 +217,18 @@ class OpTimer:
             pools = 1 if v_pool.data_ptr() == k_pool.data_ptr() else 2
             byts = float(qkv.shape[0] * seen * nkv * hd * k_pool.element_size() * pools + _nbytes(qkv) + _nbytes(out))
             flops = 4.0 * qkv.shape[0] * nq * hd * seen
+        elif name == "sigmoid_attention":
+            qkv, nq, nkv, hd = a[0], a[1], a[2], a[3]
+            kind, size, T = kw.get("mask", "causal"), int(kw.get("mask_size") or 0), qkv.shape[0]
+
+            def seen(p):                         # keys that position p sees
+                return p + 1 if kind == "causal" else (min(p + 1, size) if kind == "window" else p % size + 1)
+            if kw.get("own_rows", True):
+                flops = 4.0 * nq * hd * sum(seen(p) for p in range(T))
+            else:
+                keys = seen(max(0, self.context - 1))
+                byts = float(T * keys * nkv * hd * qkv.element_size() * 2 + _nbytes(qkv) + _nbytes(out))
+                flops = 4.0 * T * nq * hd * keys
         elif name == "gla_scan":
             proj, n_seqs, H, dim, vdim = a[0], a[10], a[11], a[12], a[13]
             T = proj.shape[0]
@@ -244,8 +256,9 @@ class OpTimer:
             T, W = x.shape
             E, ff2, _ = wgu.shape
             used = min(E, T * top)
-            flops = 2.0 * T * top * (ff2 + ff2 // 2) * W
-            byts = float(used * (ff2 + ff2 // 2) * W * wgu.element_size() + _nbytes(x) + _nbytes(out))
+            rows = ff2 + (ff2 // 2 if kw.get("gated", True) else ff2)        # rows of an expert's matrices
+            flops = 2.0 * T * top * rows * W
+            byts = float(used * rows * W * wgu.element_size() + _nbytes(x) + _nbytes(out))
         elif name in ("rope_cache_write",):
             byts = float(2 * _nbytes(a[0]))
         elif name.startswith("embed"):               # the rows that are looked up, not the table

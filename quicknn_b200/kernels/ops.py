@@ -1685,6 +1685,7 @@ def bounded_gates(rows: torch.Tensor, q_col: int, n_q: int, f_col: int, n_f: int
 # ---- attention with sigmoid weights and mixed heads ----------------------------------------------------------------------
 
 MASKS = {"causal": 0, "window": 1, "chunk": 2}
+SIGATTN_TENSOR_CORES = os.environ.get("QNN_SIGATTN", "") != "generic"
 
 
 def sigmoid_attention_refusal(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int) -> Optional[str]:
@@ -1700,13 +1701,17 @@ def sigmoid_attention_refusal(dtype: torch.dtype, n_heads: int, n_kv: int, head_
 def sigmoid_attention(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, tok_pos: torch.Tensor,
                       tok_row0: Optional[torch.Tensor], tok_slot: Optional[torch.Tensor], line, own_rows: bool,
                       mask: str, mask_size: int, scale: float, pb: Optional[torch.Tensor], talk: Optional[torch.Tensor],
-                      gate: Optional[torch.Tensor], gate_col: int = 0, splits: int = 1) -> torch.Tensor:
+                      gate: Optional[torch.Tensor], gate_col: int = 0, splits: int = 1,
+                      seq_row0: Optional[torch.Tensor] = None, seq_len: Optional[torch.Tensor] = None,
+                      longest: int = 0) -> torch.Tensor:
     """o_h(i) = sigmoid(gate[i, h]) * sum_j (sum_g talk[h, g] sigmoid(scale q_g(i) . k(j) + pb[g])) v(j) over the keys j
     that position i sees (``mask``: "causal", "window" or "chunk" of ``mask_size``).  ``qkv``: the step's packed q | k | v
     rows.  ``own_rows``: keys at or after the position of a sequence's first row of this step are read from ``qkv``,
     earlier ones from the cache ``line``; False: every key from the line (a decode step after its append).  ``gate``:
     rows whose columns ``gate_col`` .. hold one logit per head (None: no gate).  ``splits``: key ranges per token that
-    run as separate blocks and are summed in order.  Returns [rows, heads * head_dim] of qkv's type."""
+    run as separate blocks and are summed in order.  ``seq_row0`` / ``seq_len`` / ``longest``: given for whole prompts
+    (every sequence starts at position 0): bfloat16 rows with head sizes 32 to 256 then run on the tensor cores
+    (``QNN_SIGATTN=generic`` keeps the plain kernel).  Returns [rows, heads * head_dim] of qkv's type."""
     _req(qkv, "qkv", None, 2)
     _req(tok_pos, "tok_pos", torch.int32, 1)
     T = qkv.shape[0]
@@ -1733,6 +1738,17 @@ def sigmoid_attention(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
         if gate.shape[0] != T or gate_col + H > gate.shape[1]:
             raise ValueError("sigmoid_attention: a gate logit per row and head")
     out = torch.empty((T, H * D), dtype=qkv.dtype, device=qkv.device)
+    if own_rows and seq_row0 is not None and longest > 0 and qkv.dtype == torch.bfloat16 and SIGATTN_TENSOR_CORES:
+        _req(seq_row0, "seq_row0", torch.int32, 1)
+        _req(seq_len, "seq_len", torch.int32, 1)
+        code = _lib.load().qnn_sigattn_prefill_mma(
+            _p(qkv), qkv.shape[1], _p(seq_row0), _p(seq_len), seq_row0.numel(), int(longest), MASKS[mask], int(mask_size or 0),
+            float(scale), _p(pb), _p(talk), _col_ptr(gate, gate_col) if gate is not None else None,
+            dt_code(gate) if gate is not None else 0, gate.shape[1] if gate is not None else 0, _p(out), out.shape[1],
+            H, G, D, _stream())
+        if code != _lib.ERR_UNSUPPORTED:           # sizes it refuses: the plain kernel below
+            _lib.check(code, "sigmoid_attention (tensor cores)")
+            return out
     splits = max(1, int(splits))
     partial = torch.empty((splits, T, H * D), dtype=torch.float32, device=qkv.device) if splits > 1 else None
     _lib.check(_lib.load().qnn_sigattn(

@@ -15,7 +15,8 @@ mask's kind and size, the scale and the sizes is optional: ``bias``, ``qk_norm``
 
 q, k (, v) and the gate's logits are one product against the stacked matrix.  One kernel (``ops.head_prep``) adds the
 biases, copies the keys as values, rotates, norms and appends keys and values to the cache line; one kernel
-(``ops.sigmoid_attention``) does the rest for whole prompts (keys from the step's rows), for steps that continue
+(``ops.sigmoid_attention``) does the rest for whole prompts (keys from the step's rows; bfloat16 prompts at head
+sizes 32 to 256 on the tensor cores), for steps that continue
 sequences (cached keys, then the step's rows; the append comes after it, so that a ring as short as the mask is never
 overwritten under a row that still needs it) and for single tokens (keys from the line, in several ranges per
 sequence where the context is long).  The cache line keeps ``mask.size`` positions as a ring (all of them for "causal").
@@ -155,7 +156,10 @@ class SigmoidAttention(Mixer):
         a = ops.sigmoid_attention(packed, H, G, D, step.tok_pos, step.tok_row0, step.tok_slot, line, own_rows=not decode,
                                   mask=self.mask_kind, mask_size=self.mask_size, scale=self.scale, pb=self.pb,
                                   talk=self.talk, gate=p if self.out_gate else None, gate_col=gate_col,
-                                  splits=self.decode_splits(step) if decode else 1)
+                                  splits=self.decode_splits(step) if decode else 1,
+                                  seq_row0=step.seq_row0 if step.mode == "prefill" else None,
+                                  seq_len=step.seq_len if step.mode == "prefill" else None,
+                                  longest=step.max_q_len if step.mode == "prefill" else 0)
         if extend and line is not None and line.writes:
             ops.cache_append(packed, H, G, D, step.tok_pos, step.tok_slot, line)
         return project(a, self.w_o)

@@ -46,6 +46,8 @@ sigattn_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ k_
                const float* __restrict__ talk, const void* __restrict__ gate, int g_dt, long long ldg,
                T* __restrict__ out, long long ldo, float* __restrict__ partial, int n_tokens, int H, int G, int D) {
     extern __shared__ __align__(16) float sm[];
+    // bfloat16 rows in whole 16-byte pieces: keys and values are read from shared memory two at a time
+    constexpr bool PAIR = VEC && sizeof(T) == 2;
     const int HD = H * D, GD = G * D, pitch = GD + SaPad<T>::N, per = H / G;
     float* qs = sm;                                  // [H * D] queries times the scale
     float* ws = qs + HD;                             // [H][KT] weights of the tile
@@ -99,6 +101,15 @@ sigattn_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ k_
                         Vec16<T> a, b;
                         a.load(kp);
                         b.load(vp);
+                        if (PAIR) {                  // the 16 bytes as they came, four words (rows are whole words apart)
+                            const uint32_t* aw = reinterpret_cast<const uint32_t*>(&a.raw);
+                            const uint32_t* bw = reinterpret_cast<const uint32_t*>(&b.raw);
+                            uint32_t* kd = reinterpret_cast<uint32_t*>(ks + (size_t)j * pitch + c);
+                            uint32_t* vd = reinterpret_cast<uint32_t*>(vs + (size_t)j * pitch + c);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) { kd[e] = aw[e]; vd[e] = bw[e]; }
+                            continue;
+                        }
                         a.unpack(kv);
                         b.unpack(vv);
                     } else {
@@ -120,7 +131,18 @@ sigattn_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ k_
                     const float* qg = qs + g * D;
                     const T* kj = ks + (size_t)j * pitch + (g / per) * D;
                     float s = 0.f;
-                    for (int d = 0; d < D; ++d) s += qg[d] * to_f(kj[d]);
+                    if (PAIR) {
+                        const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(kj);
+                        const float2* q2 = reinterpret_cast<const float2*>(qg);
+#pragma unroll 4
+                        for (int d = 0; d < D / 2; ++d) {
+                            const float2 kf = __bfloat1622float2(k2[d]), qf = q2[d];
+                            s = fmaf(qf.x, kf.x, s);
+                            s = fmaf(qf.y, kf.y, s);
+                        }
+                    } else {
+                        for (int d = 0; d < D; ++d) s += qg[d] * to_f(kj[d]);
+                    }
                     w = 1.f / (1.f + expf(-(s + pbs[g])));
                 }
                 ws[idx] = w;
@@ -133,6 +155,26 @@ sigattn_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ k_
                 wm[idx] = m;
             }
             __syncthreads();
+            if (PAIR) {                              // accumulators 2a and 2a + 1: columns 2 idx and 2 idx + 1
+#pragma unroll
+                for (int a = 0; a < SA_NACC / 2; ++a) {
+                    const int idx = 2 * (tid + a * SA_THREADS);
+                    if (idx < HD) {
+                        const int h = idx / D, d = idx - h * D;
+                        const float* mh = wm + h * KT;
+                        const T* vc = vs + (h / per) * D + d;
+                        float s0 = acc[2 * a], s1 = acc[2 * a + 1];
+#pragma unroll 8
+                        for (int j = 0; j < KT; ++j) {
+                            const float2 vf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vc + (size_t)j * pitch));
+                            s0 = fmaf(mh[j], vf.x, s0);
+                            s1 = fmaf(mh[j], vf.y, s1);
+                        }
+                        acc[2 * a] = s0;
+                        acc[2 * a + 1] = s1;
+                    }
+                }
+            } else {
 #pragma unroll
             for (int a = 0; a < SA_NACC; ++a) {
                 const int idx = tid + a * SA_THREADS;
@@ -146,11 +188,12 @@ sigattn_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ k_
                     acc[a] = s;
                 }
             }
+            }
         }
     }
 #pragma unroll
     for (int a = 0; a < SA_NACC; ++a) {
-        const int idx = tid + a * SA_THREADS;
+        const int idx = PAIR ? 2 * (tid + (a >> 1) * SA_THREADS) + (a & 1) : tid + a * SA_THREADS;
         if (idx < HD) {
             if (n_split > 1) {
                 partial[((size_t)split * n_tokens + t) * HD + idx] = acc[a];
@@ -241,20 +284,24 @@ __device__ __forceinline__ uint32_t sa_pack_bf16(float lo, float hi) {
 
 constexpr int SAM_ROWS = 16;          // query rows of a block
 
+// Keys and values of a tile are loaded (cp.async) into one of `stages` buffers while the tile before is worked on.
+// `tiles_per_range` > 0: the key tiles of a query tile are cut into ranges of that many, a block (blockIdx.z) each; the
+// blocks leave float32 partial outputs in `partial` [ranges][rows][H * D] (zeros where a range holds no tile of the
+// query tile), which qnn_sigattn_finish's kernel sums in order: nothing is normalised over the keys, so ranges add up.
 template <int D, int KT>
 __global__ void __launch_bounds__(D > 128 ? 256 : 512)
 sigattn_prefill_mma_kernel(const bf16* __restrict__ qkv, long long ld, const int* __restrict__ seq_row0,
                            const int* __restrict__ seq_len, int mask_kind, int mask_size, float scale,
                            const float* __restrict__ pb, const float* __restrict__ talk, const void* __restrict__ gate,
-                           int g_dt, long long ldg, bf16* __restrict__ out, long long ldo, int H, int G) {
+                           int g_dt, long long ldg, bf16* __restrict__ out, long long ldo, int H, int G, int stages,
+                           int tiles_per_range, float* __restrict__ partial, int n_rows) {
     extern __shared__ __align__(16) unsigned char sa_smem_raw[];
     constexpr int WP = KT + 8;                       // pitch of a row of weights, floats
     const int HD = H * D, GD = G * D, per = H / G;
     const int QP = HD + 8, KP = GD + 8;              // pitches in elements: rows 16 bytes apart in the banks
     bf16* qs = reinterpret_cast<bf16*>(sa_smem_raw);                 // [16][QP]
-    bf16* ks = qs + (size_t)SAM_ROWS * QP;                           // [KT][KP]
-    bf16* vs = ks + (size_t)KT * KP;                                 // [KT][KP]
-    float* ws = reinterpret_cast<float*>(vs + (size_t)KT * KP);      // [H][16][WP]
+    bf16* kv = qs + (size_t)SAM_ROWS * QP;                           // [stages][keys | values][KT][KP]
+    float* ws = reinterpret_cast<float*>(kv + (size_t)stages * 2 * KT * KP);      // [H][16][WP]
     float* tk = ws + (size_t)H * SAM_ROWS * WP;                      // [H][H]
     pdl_wait();
     const int b = blockIdx.y, len = seq_len[b];
@@ -265,43 +312,53 @@ sigattn_prefill_mma_kernel(const bf16* __restrict__ qkv, long long ld, const int
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g_ = lane >> 2, t_ = lane & 3, nthr = blockDim.x;
     const int h = warp;                              // this warp's query head, and the head it mixes for
     const int c = h / per;                           // its key/value head
-    const unsigned sQ = (unsigned)__cvta_generic_to_shared(qs), sK = (unsigned)__cvta_generic_to_shared(ks);
-    const unsigned sV = (unsigned)__cvta_generic_to_shared(vs);
-    for (int i = tid; i < H * H; i += nthr) tk[i] = talk != nullptr ? talk[i] : ((i / H) == (i % H) ? 1.f : 0.f);
-    {
+    const unsigned sQ = (unsigned)__cvta_generic_to_shared(qs), sKV = (unsigned)__cvta_generic_to_shared(kv);
+    const unsigned stage_bytes = (unsigned)(2 * KT * KP) * 2, v_off = (unsigned)(KT * KP) * 2;
+    const int last = min(r0 + SAM_ROWS, len) - 1;    // the last position of the tile
+    int lo = 0;                                      // the first key that any row of the tile sees
+    if (mask_kind == QNN_MASK_WINDOW) lo = max(0, r0 - mask_size + 1);
+    else if (mask_kind == QNN_MASK_CHUNK) lo = (r0 / mask_size) * mask_size;
+    const int all_tiles = (last - lo) / KT + 1;
+    const int kt0 = tiles_per_range > 0 ? (int)blockIdx.z * tiles_per_range : 0;
+    const int kt1 = tiles_per_range > 0 ? min(all_tiles, kt0 + tiles_per_range) : all_tiles;
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
+    auto load_kv = [&](int kt, int stage) {
+        const int j0 = lo + kt * KT, chunks = GD / 8;
+        const unsigned dst = sKV + stage * stage_bytes;
+        for (int idx = tid; idx < KT * chunks; idx += nthr) {
+            const int row = idx / chunks, ch = idx - row * chunks;
+            const bool valid = j0 + row <= last;
+            const bf16* src = qkv + (size_t)(row0 + (valid ? j0 + row : 0)) * ld + HD + ch * 8;
+            sa_cp_async_16(dst + (unsigned)(row * KP + ch * 8) * 2, src, valid);
+            sa_cp_async_16(dst + v_off + (unsigned)(row * KP + ch * 8) * 2, src + GD, valid);
+        }
+    };
+    if (kt0 < kt1) {
+        for (int i = tid; i < H * H; i += nthr) tk[i] = talk != nullptr ? talk[i] : ((i / H) == (i % H) ? 1.f : 0.f);
         const int chunks = HD / 8;
         for (int idx = tid; idx < SAM_ROWS * chunks; idx += nthr) {
             const int row = idx / chunks, ch = idx - row * chunks;
             const bool valid = r0 + row < len;
             sa_cp_async_16(sQ + (unsigned)(row * QP + ch * 8) * 2, qkv + (size_t)(row0 + (valid ? r0 + row : 0)) * ld + ch * 8, valid);
         }
+        load_kv(kt0, 0);
+        asm volatile("cp.async.commit_group;\n" ::);
     }
-    const int last = min(r0 + SAM_ROWS, len) - 1;    // the last position of the tile
-    int lo = 0;                                      // the first key that any row of the tile sees
-    if (mask_kind == QNN_MASK_WINDOW) lo = max(0, r0 - mask_size + 1);
-    else if (mask_kind == QNN_MASK_CHUNK) lo = (r0 / mask_size) * mask_size;
-    const int n_tiles = (last - lo) / KT + 1;
     const float bias = pb != nullptr ? pb[h] : 0.f;
-    float o[D / 8][4];
-#pragma unroll
-    for (int i = 0; i < D / 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) o[i][j] = 0.f;
-    for (int kt = 0; kt < n_tiles; ++kt) {
+    for (int kt = kt0; kt < kt1; ++kt) {
         const int j0 = lo + kt * KT;
-        __syncthreads();                             // the tile before is read
-        {
-            const int chunks = GD / 8;
-            for (int idx = tid; idx < KT * chunks; idx += nthr) {
-                const int row = idx / chunks, ch = idx - row * chunks;
-                const bool valid = j0 + row <= last;
-                const bf16* src = qkv + (size_t)(row0 + (valid ? j0 + row : 0)) * ld + HD + ch * 8;
-                sa_cp_async_16(sK + (unsigned)(row * KP + ch * 8) * 2, src, valid);
-                sa_cp_async_16(sV + (unsigned)(row * KP + ch * 8) * 2, src + GD, valid);
-            }
+        const int stage = stages > 1 ? ((kt - kt0) & 1) : 0;
+        asm volatile("cp.async.wait_group 0;\n" ::);
+        __syncthreads();                             // this tile has come; the tile before is read, its weights too
+        if (stages > 1 && kt + 1 < kt1) {
+            load_kv(kt + 1, stage ^ 1);
+            asm volatile("cp.async.commit_group;\n" ::);
         }
-        sa_cp_async_wait_all();
-        __syncthreads();
+        const unsigned sK = sKV + stage * stage_bytes, sV = sK + v_off;
         // the scores of this warp's head
         float s[KT / 8][4];
 #pragma unroll
@@ -334,7 +391,7 @@ sigattn_prefill_mma_kernel(const bf16* __restrict__ qkv, long long ld, const int
                 for (int e = 0; e < 2; ++e) {
                     const int j = j0 + nt * 8 + 2 * t_ + e;
                     const bool seen = j <= i && j >= first && i < len;
-                    w2[e] = seen ? 1.f / (1.f + __expf(-(s[nt][half * 2 + e] * scale + bias))) : 0.f;
+                    w2[e] = seen ? __fdividef(1.f, 1.f + __expf(-(s[nt][half * 2 + e] * scale + bias))) : 0.f;
                 }
                 *reinterpret_cast<float2*>(ws + ((size_t)h * SAM_ROWS + row) * WP + nt * 8 + 2 * t_) = make_float2(w2[0], w2[1]);
             }
@@ -369,12 +426,24 @@ sigattn_prefill_mma_kernel(const bf16* __restrict__ qkv, long long ld, const int
                 sa_mma_16816(o[dp * 2 + 1], a, bfr[2], bfr[3]);
             }
         }
+        if (stages == 1 && kt + 1 < kt1) {
+            __syncthreads();                         // the one buffer is read before it is filled again
+            load_kv(kt + 1, 0);
+            asm volatile("cp.async.commit_group;\n" ::);
+        }
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int i = r0 + g_ + half * 8;
         if (i >= len) continue;
         const size_t t = (size_t)(row0 + i);
+        if (tiles_per_range > 0) {
+            float* dst = partial + ((size_t)blockIdx.z * n_rows + t) * HD + h * D + 2 * t_;
+#pragma unroll
+            for (int nd = 0; nd < D / 8; ++nd)
+                *reinterpret_cast<float2*>(dst + nd * 8) = make_float2(o[nd][half * 2], o[nd][half * 2 + 1]);
+            continue;
+        }
         float gt = 1.f;
         if (gate != nullptr) gt = 1.f / (1.f + expf(-load_as_f(gate, g_dt, t * ldg + h)));
 #pragma unroll
@@ -384,15 +453,31 @@ sigattn_prefill_mma_kernel(const bf16* __restrict__ qkv, long long ld, const int
     }
 }
 
-size_t sam_smem(int H, int G, int D, int KT) {
-    return ((size_t)SAM_ROWS * (H * D + 8) + 2 * (size_t)KT * (G * D + 8)) * 2 +
+size_t sam_smem(int H, int G, int D, int KT, int stages) {
+    return ((size_t)SAM_ROWS * (H * D + 8) + (size_t)stages * 2 * KT * (G * D + 8)) * 2 +
            ((size_t)H * SAM_ROWS * (KT + 8) + (size_t)H * H) * sizeof(float);
+}
+
+// Keys per tile: 32 where two blocks of that size fit an SM together or where tiles of 16 would not let two fit either;
+// else 16 (two blocks per SM hide each other's barriers and loads).  QNN_SIGATTN_KT=16|32 fixes it, for measurements.
+int sam_tile(int H, int G, int D) {
+    static int fixed = -1;
+    if (fixed < 0) {
+        const char* e = getenv("QNN_SIGATTN_KT");
+        fixed = e != nullptr ? atoi(e) : 0;
+    }
+    if (fixed == 16 || fixed == 32) return sam_smem(H, G, D, fixed, 1) <= 220 * 1024 ? fixed : 16;
+    const size_t half = 113 * 1024;
+    if (sam_smem(H, G, D, 32, 2) <= half) return 32;
+    if (sam_smem(H, G, D, 16, 2) <= half) return 16;
+    return sam_smem(H, G, D, 32, 2) <= 220 * 1024 ? 32 : 16;
 }
 
 template <int D, int KT>
 int sam_launch(dim3 grid, int threads, size_t smem, cudaStream_t st, const void* qkv, long long ld, const int* seq_row0,
                const int* seq_len, int mask_kind, int mask_size, float scale, const float* pb, const float* talk,
-               const void* gate, int g_dt, long long ldg, void* out, long long ldo, int H, int G) {
+               const void* gate, int g_dt, long long ldg, void* out, long long ldo, int H, int G, int stages,
+               int tiles_per_range, float* partial, int n_rows) {
     static size_t allowed = 48 * 1024;
     if (smem > allowed) {
         const cudaError_t rc = cudaFuncSetAttribute(sigattn_prefill_mma_kernel<D, KT>,
@@ -401,7 +486,8 @@ int sam_launch(dim3 grid, int threads, size_t smem, cudaStream_t st, const void*
         allowed = smem;
     }
     launch_pdl(sigattn_prefill_mma_kernel<D, KT>, grid, dim3(threads), smem, st, (const bf16*)qkv, ld, seq_row0, seq_len,
-               mask_kind, mask_size, scale, pb, talk, gate, g_dt, ldg, (bf16*)out, ldo, H, G);
+               mask_kind, mask_size, scale, pb, talk, gate, g_dt, ldg, (bf16*)out, ldo, H, G, stages, tiles_per_range,
+               partial, n_rows);
     QNN_LAUNCH_CHECK();
 }
 
@@ -465,31 +551,52 @@ QNN_API int qnn_sigattn(const void* qkv, int dtype, long long ld, const void* k_
 
 // Whole prompts (every sequence of the step starts at position 0) in bfloat16 on the tensor cores.  qkv, pb, talk, gate
 // and out as for qnn_sigattn; seq_row0 / seq_len: first row and length of each of the B sequences; longest: the longest
-// of them.  Head sizes 32, 64, 128 (up to 16 heads) and 256 (up to 8 heads), rows in whole 16-byte pieces; anything
-// else is refused with QNN_ERR_UNSUPPORTED and the caller takes qnn_sigattn.
+// of them; T: rows of the step.  Head sizes 32, 64, 128 (up to 16 heads) and 256 (up to 8 heads), rows in whole 16-byte
+// pieces; anything else is refused with QNN_ERR_UNSUPPORTED and the caller takes qnn_sigattn.  Where a query tile sees
+// many key tiles they are cut into ranges that run as blocks of their own (qnn_sigattn_prefill_ranges says how many
+// for given sizes); `partial` then holds float32 [ranges, T, H * D].
+QNN_API int qnn_sigattn_prefill_ranges(int longest, int mask_kind, int mask_size, int H, int G, int D, int* tiles_per_range) {
+    const int KT = sam_tile(H, G, D);
+    int keys = longest;                              // the most keys that a query tile walks
+    if (mask_kind != QNN_MASK_CAUSAL) keys = longest < mask_size + SAM_ROWS ? longest : mask_size + SAM_ROWS;
+    const int tiles = (keys + KT - 1) / KT + 1;
+    const int per = 512 / KT;                        // a range: 512 keys
+    *tiles_per_range = tiles > per + per / 2 ? per : 0;
+    return *tiles_per_range > 0 ? (tiles + per - 1) / per : 1;
+}
+
 QNN_API int qnn_sigattn_prefill_mma(const void* qkv, long long ld, const int* seq_row0, const int* seq_len, int B,
                                     int longest, int mask_kind, int mask_size, float scale, const float* pb,
                                     const float* talk, const void* gate, int g_dt, long long ldg, void* out,
-                                    long long ldo, int H, int G, int D, cudaStream_t st) {
+                                    long long ldo, int H, int G, int D, float* partial, int T, cudaStream_t st) {
     if (B <= 0 || longest <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || H > (D > 128 ? 8 : 16)) return QNN_ERR_UNSUPPORTED;
     if (D != 32 && D != 64 && D != 128 && D != 256) return QNN_ERR_UNSUPPORTED;
     if (ld % 8 || ldo % 2 || ((uintptr_t)qkv % 16) || ((uintptr_t)out % 4) || B > 65535) return QNN_ERR_UNSUPPORTED;
     if (mask_kind < 0 || mask_kind > 2 || (mask_kind != QNN_MASK_CAUSAL && mask_size < 1)) return QNN_ERR_ARGUMENT;
     if (seq_row0 == nullptr || seq_len == nullptr) return QNN_ERR_ARGUMENT;
-    int KT = 32;
-    if (sam_smem(H, G, D, KT) > 220 * 1024) KT = 16;
-    const size_t smem = sam_smem(H, G, D, KT);
+    int KT = sam_tile(H, G, D), stages = 2;
+    if (sam_smem(H, G, D, KT, stages) > 220 * 1024) stages = 1;
+    const size_t smem = sam_smem(H, G, D, KT, stages);
     if (smem > 220 * 1024) return QNN_ERR_UNSUPPORTED;
-    const dim3 grid((longest + SAM_ROWS - 1) / SAM_ROWS, B);
+    int tiles_per_range = 0;
+    const int ranges = qnn_sigattn_prefill_ranges(longest, mask_kind, mask_size, H, G, D, &tiles_per_range);
+    if (ranges > 1 && partial == nullptr) return QNN_ERR_ARGUMENT;
+    const dim3 grid((longest + SAM_ROWS - 1) / SAM_ROWS, B, ranges);
+    int rc;
 #define QNN_SAM(DV)                                                                                                   \
-    return KT == 32 ? sam_launch<DV, 32>(grid, H * 32, smem, st, qkv, ld, seq_row0, seq_len, mask_kind, mask_size, scale, \
-                                         pb, talk, gate, g_dt, ldg, out, ldo, H, G)                                   \
-                    : sam_launch<DV, 16>(grid, H * 32, smem, st, qkv, ld, seq_row0, seq_len, mask_kind, mask_size, scale, \
-                                         pb, talk, gate, g_dt, ldg, out, ldo, H, G)
+    rc = KT == 32 ? sam_launch<DV, 32>(grid, H * 32, smem, st, qkv, ld, seq_row0, seq_len, mask_kind, mask_size, scale,   \
+                                       pb, talk, gate, g_dt, ldg, out, ldo, H, G, stages, tiles_per_range, partial, T)   \
+                  : sam_launch<DV, 16>(grid, H * 32, smem, st, qkv, ld, seq_row0, seq_len, mask_kind, mask_size, scale,   \
+                                       pb, talk, gate, g_dt, ldg, out, ldo, H, G, stages, tiles_per_range, partial, T)
     if (D == 32) QNN_SAM(32);
-    if (D == 64) QNN_SAM(64);
-    if (D == 128) QNN_SAM(128);
-    QNN_SAM(256);
+    else if (D == 64) QNN_SAM(64);
+    else if (D == 128) QNN_SAM(128);
+    else QNN_SAM(256);
 #undef QNN_SAM
+    if (rc != 0 || ranges == 1) return rc;
+    const size_t n = (size_t)T * H * D;
+    launch_pdl(sigattn_finish_kernel<bf16>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (const float*)partial, ranges,
+               gate, g_dt, ldg, (bf16*)out, ldo, T, H * D, D);
+    QNN_LAUNCH_CHECK();
 }

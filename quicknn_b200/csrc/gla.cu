@@ -270,6 +270,36 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ o, long long ldo
     }
 }
 
+// The same for heads so wide that a warp would walk them for long (one norm over all heads of a row, handed in as a
+// single head): a block per (row, head), the row's sum by all its warps in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_norm_gate_wide_kernel(const float* __restrict__ o, long long ldo, int hs, const float* __restrict__ den,
+                           long long ldden, const void* __restrict__ w, int w_dt, int w_mode, float eps,
+                           const T* __restrict__ g, long long ldg, int gate_act, T* __restrict__ out, long long ld_out,
+                           int rows, int H, int vdim) {
+    __shared__ float red[32];
+    pdl_wait();
+    const int unit = blockIdx.x;
+    const int t = unit / H, h = unit - t * H;
+    const float* orow = o + (size_t)t * ldo + (size_t)h * hs;
+    float scale = 1.f;
+    if (den != nullptr) scale = 1.f / (fmaxf(fabsf(orow[vdim]), den[(size_t)t * ldden + h]) + 1e-6f);
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < vdim; j += blockDim.x) {
+        const float v = orow[j] * scale;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)vdim + eps);
+    for (int j = threadIdx.x; j < vdim; j += blockDim.x) {
+        const float gv = gate_act == 2 ? 0.f : to_f(g[(size_t)t * ldg + h * vdim + j]);
+        const float wv = w_mode == 0 ? 1.f : load_as_f(w, w_dt, w_mode == 2 ? (size_t)h * vdim + j : (size_t)j);
+        const float ga = gate_act == 2 ? 1.f : (gate_act == 1 ? 1.f / (1.f + expf(-gv)) : silu(gv));
+        out[(size_t)t * ld_out + h * vdim + j] = from_f<T>(orow[j] * scale * inv * wv * ga);
+    }
+}
+
 // ---- gates of a matrix memory with a running maximum ---------------------------------------------------------------
 // pre: float32 [rows, ldp] with the input gate's pre-activation of head h at column h and the forget gate's at H + h;
 // bias: [2H] (input gates, then forget gates).  i = cap tanh((pre_i + b_i) / cap); f = log sigmoid(cap tanh((pre_f +
@@ -505,6 +535,16 @@ QNN_API int qnn_head_norm_gate(const float* o, long long ldo, int hs, const floa
     if (H <= 0 || vdim <= 0 || hs < vdim || (den != nullptr && hs <= vdim) || (w_mode != 0 && w == nullptr))
         return QNN_ERR_ARGUMENT;
     if (gate_act < 0 || gate_act > 2 || (gate_act != 2 && g == nullptr)) return QNN_ERR_ARGUMENT;      // 2: no gate
+    if (vdim >= 512 && (long long)rows * H <= 0x7fffffffLL) {         // a block per (row, head)
+        const dim3 wide((unsigned)(rows * H));
+        if (dtype == QNN_DT_BF16)
+            launch_pdl(head_norm_gate_wide_kernel<bf16>, wide, dim3(256), 0, st, o, ldo, hs, den, ldden, w, w_dt, w_mode, eps,
+                       (const bf16*)g, ldg, gate_act, (bf16*)out, ld_out, rows, H, vdim);
+        else
+            launch_pdl(head_norm_gate_wide_kernel<float>, wide, dim3(256), 0, st, o, ldo, hs, den, ldden, w, w_dt, w_mode, eps,
+                       (const float*)g, ldg, gate_act, (float*)out, ld_out, rows, H, vdim);
+        QNN_LAUNCH_CHECK();
+    }
     const int warps = 4;
     const dim3 grid(((size_t)rows * H + warps - 1) / warps);
     if (dtype == QNN_DT_BF16)

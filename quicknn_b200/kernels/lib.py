@@ -115,7 +115,8 @@ _SIGNATURES: Dict[str, list] = {
     "qnn_sigattn": [c_vp, c_int, c_ll, c_vp, c_vp, c_vp, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_int, c_int, c_int,
                     c_float, c_vp, c_vp, c_vp, c_int, c_ll, c_vp, c_ll, c_vp, c_int, c_int, c_int, c_int, c_int, c_vp],
     "qnn_sigattn_prefill_mma": [c_vp, c_ll, c_vp, c_vp, c_int, c_int, c_int, c_int, c_float, c_vp, c_vp, c_vp, c_int, c_ll,
-                                c_vp, c_ll, c_int, c_int, c_int, c_vp],
+                                c_vp, c_ll, c_int, c_int, c_int, c_vp, c_int, c_vp],
+    "qnn_sigattn_prefill_ranges": [c_int, c_int, c_int, c_int, c_int, c_int, c_vp],
     "qnn_head_norm_gate": [c_vp, c_ll, c_int, c_vp, c_ll, c_vp, c_int, c_int, c_float, c_vp, c_ll, c_int, c_vp, c_ll,
                            c_int, c_int, c_int, c_int, c_vp],
 }

@@ -1741,11 +1741,16 @@ def sigmoid_attention(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
     if own_rows and seq_row0 is not None and longest > 0 and qkv.dtype == torch.bfloat16 and SIGATTN_TENSOR_CORES:
         _req(seq_row0, "seq_row0", torch.int32, 1)
         _req(seq_len, "seq_len", torch.int32, 1)
+        # a query tile that sees many key tiles has them walked in ranges, by blocks of their own
+        per_range = ctypes.c_int(0)
+        ranges = _lib.load().qnn_sigattn_prefill_ranges(int(longest), MASKS[mask], int(mask_size or 0), H, G, D,
+                                                        ctypes.byref(per_range))
+        part = torch.empty((ranges, T, H * D), dtype=torch.float32, device=qkv.device) if ranges > 1 else None
         code = _lib.load().qnn_sigattn_prefill_mma(
             _p(qkv), qkv.shape[1], _p(seq_row0), _p(seq_len), seq_row0.numel(), int(longest), MASKS[mask], int(mask_size or 0),
             float(scale), _p(pb), _p(talk), _col_ptr(gate, gate_col) if gate is not None else None,
             dt_code(gate) if gate is not None else 0, gate.shape[1] if gate is not None else 0, _p(out), out.shape[1],
-            H, G, D, _stream())
+            H, G, D, _p(part), T, _stream())
         if code != _lib.ERR_UNSUPPORTED:           # sizes it refuses: the plain kernel below
             _lib.check(code, "sigmoid_attention (tensor cores)")
             return out

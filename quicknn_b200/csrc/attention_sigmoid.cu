@@ -34,6 +34,15 @@ namespace {
 constexpr int SA_THREADS = 256;
 constexpr int SA_NACC = 16;                         // outputs per thread: heads * head size up to 4096
 
+__device__ __forceinline__ void sa_cp_async_16(unsigned smem_dst, const void* gmem_src, bool valid) {
+    const int bytes = valid ? 16 : 0;                // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_dst), "l"(gmem_src), "r"(bytes));
+}
+__device__ __forceinline__ void sa_cp_async_wait_all() {
+    asm volatile("cp.async.commit_group;\n" ::);
+    asm volatile("cp.async.wait_group 0;\n" ::);
+}
+
 template <typename T> struct SaPad { static constexpr int N = 1; };
 template <> struct SaPad<bf16> { static constexpr int N = 2; };      // rows of the tiles an odd number of words apart
 
@@ -48,13 +57,14 @@ sigattn_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ k_
     extern __shared__ __align__(16) float sm[];
     // bfloat16 rows in whole 16-byte pieces: keys and values are read from shared memory two at a time
     constexpr bool PAIR = VEC && sizeof(T) == 2;
-    const int HD = H * D, GD = G * D, pitch = GD + SaPad<T>::N, per = H / G;
+    // VEC: rows of the tiles start on 16 bytes (they are filled by cp.async); else rows an odd number of words apart
+    const int HD = H * D, GD = G * D, pitch = GD + (VEC ? (int)(16 / sizeof(T)) : SaPad<T>::N), per = H / G;
     float* qs = sm;                                  // [H * D] queries times the scale
     float* ws = qs + HD;                             // [H][KT] weights of the tile
     float* wm = ws + H * KT;                         // [H][KT] mixed over heads
     float* tk = wm + H * KT;                         // [H][H]
     float* pbs = tk + H * H;                         // [H]
-    T* ks = reinterpret_cast<T*>(pbs + H + (H & 1)); // [KT][pitch]
+    T* ks = reinterpret_cast<T*>(sm + ((HD + 2 * H * KT + H * H + H + 3) & ~3));   // [KT][pitch], on 16 bytes
     T* vs = ks + (size_t)KT * pitch;
     pdl_wait();
     const int t = blockIdx.x, split = blockIdx.y, n_split = gridDim.y;
@@ -79,6 +89,36 @@ sigattn_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ k_
         for (int kt = split; kt < n_tiles; kt += n_split) {
             const int j0 = lo + kt * KT, nk = min(KT, pos + 1 - j0);
             __syncthreads();
+            if (VEC) {
+                // a warp per key row: the row's place is worked out once, its pieces go global -> shared by cp.async
+                const int warp = tid >> 5, lane = tid & 31;
+                const unsigned sk = (unsigned)__cvta_generic_to_shared(ks), sv = (unsigned)__cvta_generic_to_shared(vs);
+                constexpr int PIECE = 16 / sizeof(T);
+                for (int j = warp; j < KT; j += SA_THREADS / 32) {
+                    const bool valid = j < nk;
+                    const int p = j0 + j;
+                    const T *kp = qkv, *vp = qkv;
+                    size_t head_step = D;             // from one key/value head's columns to the next's
+                    if (valid && p >= pos0) {
+                        kp = qkv + (size_t)(row0 + p - pos0) * ld + HD;
+                        vp = kp + GD;
+                    } else if (valid) {
+                        const int r = ring > 0 ? p % ring : p;
+                        const int page = page_table[(size_t)slot * max_pages + r / page_size];
+                        const size_t at = ((size_t)page * G * page_size + (r % page_size)) * D;
+                        kp = k_pool + at;
+                        vp = v_pool + at;
+                        head_step = (size_t)page_size * D;
+                    }
+                    for (int c = 0; c < G; ++c)
+                        for (int d = lane * PIECE; d < D; d += 32 * PIECE) {
+                            const unsigned dst = (unsigned)(((size_t)j * pitch + c * D + d) * sizeof(T));
+                            sa_cp_async_16(sk + dst, kp + c * head_step + d, valid);
+                            sa_cp_async_16(sv + dst, vp + c * head_step + d, valid);
+                        }
+                }
+                sa_cp_async_wait_all();
+            } else
             for (int idx = tid; idx < KT * chunks; idx += SA_THREADS) {
                 const int j = idx / chunks, c = (idx - j * chunks) * V;
                 float kv[V], vv[V];
@@ -124,6 +164,33 @@ sigattn_kernel(const T* __restrict__ qkv, long long ld, const T* __restrict__ k_
                 }
             }
             __syncthreads();
+            if (VEC) {
+                // a lane per score, as below; rows start on 16 bytes here, so lane j begins its walk along the head
+                // (j / 8) pairs further on and wraps: the 32 lanes of a key tile then read 32 different banks
+                for (int idx = tid; idx < H * KT; idx += SA_THREADS) {
+                    const int g = idx / KT, j = idx - g * KT;
+                    float w = 0.f;
+                    if (j < nk) {
+                        const float2* q2 = reinterpret_cast<const float2*>(qs + g * D);
+                        const T* kj = ks + (size_t)j * pitch + (g / per) * D;
+                        const int half = D / 2;
+                        int e = (j >> 3) & 3;
+                        if (e >= half) e = 0;
+                        float sc = 0.f;
+                        for (int n = 0; n < half; ++n) {
+                            float2 kf;
+                            if (sizeof(T) == 2) kf = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(kj)[e]);
+                            else kf = reinterpret_cast<const float2*>(kj)[e];
+                            const float2 qf = q2[e];
+                            sc = fmaf(qf.x, kf.x, sc);
+                            sc = fmaf(qf.y, kf.y, sc);
+                            if (++e == half) e = 0;
+                        }
+                        w = 1.f / (1.f + expf(-(sc + pbs[g])));
+                    }
+                    ws[idx] = w;
+                }
+            } else
             for (int idx = tid; idx < H * KT; idx += SA_THREADS) {
                 const int g = idx / KT, j = idx - g * KT;
                 float w = 0.f;
@@ -221,9 +288,10 @@ __global__ void sigattn_finish_kernel(const float* __restrict__ partial, int n_s
     out[t * ldo + idx] = from_f<T>(v);
 }
 
-size_t sa_smem(int H, int G, int D, int KT, size_t elem) {
-    const size_t pitch = (size_t)G * D + (elem == 2 ? 2 : 1);
-    return ((size_t)H * D + 2 * (size_t)H * KT + (size_t)H * H + H + (H & 1)) * sizeof(float) + 2 * (size_t)KT * pitch * elem;
+size_t sa_smem(int H, int G, int D, int KT, size_t elem, bool vec = true) {
+    const size_t pitch = (size_t)G * D + (vec ? 16 / elem : (elem == 2 ? 2 : 1));        // the wider of the two when asked in general
+    const size_t floats = ((size_t)H * D + 2 * (size_t)H * KT + (size_t)H * H + H + 3) & ~(size_t)3;
+    return floats * sizeof(float) + 2 * (size_t)KT * pitch * elem;
 }
 
 template <typename T, int KT, bool VEC>
@@ -255,14 +323,6 @@ int sa_launch(dim3 grid, size_t smem, cudaStream_t st, const void* qkv, long lon
 // memory).  Keys and values are read from the step's packed rows.  The mixed weights are rounded to bfloat16 for the
 // product with the values, as the softmax kernels round theirs; sums are float32.
 
-__device__ __forceinline__ void sa_cp_async_16(unsigned smem_dst, const void* gmem_src, bool valid) {
-    const int bytes = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_dst), "l"(gmem_src), "r"(bytes));
-}
-__device__ __forceinline__ void sa_cp_async_wait_all() {
-    asm volatile("cp.async.commit_group;\n" ::);
-    asm volatile("cp.async.wait_group 0;\n" ::);
-}
 __device__ __forceinline__ void sa_ldmatrix_x4(uint32_t (&r)[4], unsigned addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -518,11 +578,11 @@ QNN_API int qnn_sigattn(const void* qkv, int dtype, long long ld, const void* k_
     if (tok_pos == nullptr || (own_rows && tok_row0 == nullptr) || (n_split > 1 && partial == nullptr)) return QNN_ERR_ARGUMENT;
     if (!own_rows && (k_pool == nullptr || v_pool == nullptr || page_table == nullptr)) return QNN_ERR_ARGUMENT;
     const size_t elem = dtype == QNN_DT_BF16 ? 2 : 4;
-    int KT = 32;
-    while (KT > 8 && sa_smem(H, G, D, KT, elem) > 200 * 1024) KT /= 2;
-    const size_t smem = sa_smem(H, G, D, KT, elem);
     const bool vec = (D * elem) % 16 == 0 && (ld * elem) % 16 == 0 && ((uintptr_t)qkv % 16) == 0 &&
                      ((uintptr_t)k_pool % 16) == 0 && ((uintptr_t)v_pool % 16) == 0;
+    int KT = 32;
+    while (KT > 8 && sa_smem(H, G, D, KT, elem, vec) > 200 * 1024) KT /= 2;
+    const size_t smem = sa_smem(H, G, D, KT, elem, vec);
     const dim3 grid(T, n_split);
     int rc;
 #define QNN_SA(TT, KTV)                                                                                               \

@@ -33,7 +33,7 @@ from .base import MIXERS, POSITIONS, CacheNeed, Mixer
 from .linear import project, stack_rows
 from .spec import PartSpec
 
-TILES_PER_RANGE = 4          # key tiles of 32 that a block of a decode step walks at least, where the context is long
+TILES_PER_RANGE = 2          # key tiles of 32 that a block of a decode step walks at least, where the context is long
 
 
 @MIXERS.register("sigmoid_attention")

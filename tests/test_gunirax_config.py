@@ -132,15 +132,15 @@ def test_a_random_folder_loads_and_the_plain_model_reads_it(tmp_path):
 def test_rotary_frequencies_of_the_library_are_the_plain_ones():
     from quicknn_b200.config.tumudra import RotaryConfig
     from quicknn_b200.parts import POSITIONS
-    for rot in ({"base": 50000.0, "dims": 32, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 256}},
+    for rot in ({"base": 20000.0, "dims": 32, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 256}},
                 {"base": 100.0, "dims": 6}, {"base": 1e6, "dims": 64, "scaling": {"factor": 32.0, "low": 2.0, "high": 3.0,
                                                                                   "original": 8192}}):
         part = RotaryConfig.parse(rot, "rot").part(64, "interleaved")
         got = POSITIONS.get(part.kind)(part).frequencies().numpy()
         assert np.allclose(got, GP.rotary_frequencies(rot), rtol=1e-12, atol=0)
     # the three regimes are all met by the first case: kept, divided, blended
-    f0 = 50000.0 ** (-2.0 * np.arange(16) / 32)
-    f = GP.rotary_frequencies({"base": 50000.0, "dims": 32, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 256}})
+    f0 = 20000.0 ** (-2.0 * np.arange(16) / 32)
+    f = GP.rotary_frequencies({"base": 20000.0, "dims": 32, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 256}})
     ratio = f / f0
     assert (ratio == 1.0).any() and np.isclose(ratio, 0.25).any() and ((ratio > 0.26) & (ratio < 0.99)).any()
 
